@@ -111,6 +111,123 @@ class TwinOps:
             for t in ids[c:d]:
                 logits[r, t] = float("-inf")
 
+    # -- the kernels of the stream norm, the linear-attention mixer, the two-map attention and the routed
+    # feed-forward (formulas restated from the kernels' own headers) ------------------------------------------
+    def rmsnorm_stream(self, out, stream, add1, add2, weight, eps, first=False):
+        total = torch.zeros_like(stream) if first else stream.clone()
+        for a in (add1, add2):
+            if a is not None:
+                total = total + a.float()
+        stream.copy_(total)
+        if out is not None:
+            out.copy_((total / torch.sqrt(total.pow(2).mean(-1, keepdim=True) + eps) * weight.float()).to(out.dtype))
+
+    def gated_rmsnorm(self, out, x, gate, weight, eps):
+        y = x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + eps) * weight.float()
+        out.copy_((y * torch.sigmoid(gate.float())).to(out.dtype))
+
+    def activation(self, out, x, kind):
+        z = x.float()
+        if kind == "gelu_tanh":
+            y = 0.5 * z * (1.0 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z ** 3)))
+        elif kind == "relu2":
+            y = torch.relu(z) ** 2
+        else:
+            y = F.silu(z)
+        out.copy_(y.to(out.dtype))
+
+    def lightning(self, out, proj, state, decay, step, H, D, V):
+        qs = step.q_start.tolist()
+        slots = step.state_slots.tolist()
+        act = lambda t: F.silu(t.float()).to(proj.dtype).float()
+        q = act(proj[:, : H * D]).view(-1, H, D)
+        k = act(proj[:, H * D: 2 * H * D]).view(-1, H, D)
+        v = act(proj[:, 2 * H * D: 2 * H * D + H * V]).view(-1, H, V)
+        for b in range(step.num_requests):
+            S = state[slots[b]]
+            for t in range(qs[b], qs[b + 1]):
+                S.mul_(decay[:, None, None]).add_(k[t, :, :, None] * v[t, :, None, :])
+                out[t] = torch.einsum("hdv,hd->hv", S, q[t]).reshape(-1)
+
+    def kv_write_pair(self, proj, k_off, v_off, k_cache, v_cache, slots, KVH, DK, DV, page_size):
+        m = slots >= 0
+        sl = slots[m].long()
+        k_cache[sl // page_size, :, sl % page_size, :] = proj[m, k_off:k_off + KVH * DK].view(-1, KVH, DK)
+        v_cache[sl // page_size, :, sl % page_size, :] = proj[m, v_off:v_off + KVH * DV].view(-1, KVH, DV)
+
+    def attention_diff(self, out, proj, k_cache, v_cache, block_tables, step, H, KVH, D, V, page_size, scale, lam,
+                       eps, out_scale):
+        qsl = step.q_start.tolist()
+        G = H // KVH
+        out.zero_()
+        for b, seq_len in enumerate(step.seq_lens.tolist()):
+            qs, qe = qsl[b], qsl[b + 1]
+            if seq_len == 0 or qe == qs:
+                continue
+            Tq = qe - qs
+            nb = -(-seq_len // page_size)
+            blocks = block_tables[b, :nb].long()
+            kk = k_cache[blocks].permute(0, 2, 1, 3).reshape(nb * page_size, KVH, 2, D)[:seq_len].float()
+            vv = v_cache[blocks].permute(0, 2, 1, 3).reshape(nb * page_size, KVH, V)[:seq_len].float()
+            q = proj[qs:qe, : H * 2 * D].view(Tq, H, 2, D).float()
+            i = torch.arange(Tq)[:, None] + (seq_len - Tq)
+            ok = torch.arange(seq_len)[None, :] <= i
+            for h in range(H):
+                maps = []
+                for c in range(2):
+                    s = (q[:, h, c] @ kk[:, h // G, c].t()) * scale
+                    maps.append(torch.softmax(s.masked_fill(~ok, float("-inf")), -1) @ vv[:, h // G])
+                o = maps[0] - lam * maps[1]
+                o = o / torch.sqrt(o.pow(2).mean(-1, keepdim=True) + eps) * out_scale
+                out[qs:qe, h * V:(h + 1) * V] = o.to(out.dtype)
+
+    def router_topk(self, idx, weights, x, w_router, softmax, renormalize):
+        z = F.linear(x.float(), w_router.float())
+        scores = torch.softmax(z, -1) if softmax else torch.sigmoid(z)
+        best = z.topk(idx.shape[1], dim=-1)
+        idx.copy_(best.indices.to(torch.int32))
+        w = scores.gather(1, best.indices)
+        weights.copy_(w / w.sum(-1, keepdim=True) if renormalize else w)
+
+    def moe_align(self, idx, E):
+        flat = idx.reshape(-1).long()
+        order = torch.sort(flat, stable=True).indices.to(torch.int32)
+        place = torch.empty_like(order)
+        place[order.long()] = torch.arange(order.numel(), dtype=torch.int32)
+        counts = torch.bincount(flat, minlength=E)
+        offsets = torch.cat([torch.zeros(1, dtype=torch.long), counts.cumsum(0)]).to(torch.int32)
+        return offsets, order, place, None
+
+    def grouped_linear(self, out, x, w, order, row_scale, offsets, tiles, top, act="none"):
+        off = offsets.tolist()
+        for e in range(w.shape[0]):
+            a, b = off[e], off[e + 1]
+            if a == b:
+                continue
+            if order is None:
+                rows = x[a:b].float()
+            else:
+                pairs = order[a:b].long()
+                rows = x[pairs // top].float()
+                if row_scale is not None:
+                    rows = (rows * row_scale.reshape(-1)[pairs][:, None]).to(x.dtype).float()
+            y = F.linear(rows, w[e].float())
+            tmp = torch.empty_like(y)
+            if act == "none":
+                tmp = y
+            else:
+                self.activation(tmp, y, act)
+            out[a:b] = tmp.to(out.dtype)
+
+    def moe_combine(self, out, y, place, pair_weights, top):
+        rows = y[place.long()].view(out.shape[0], top, -1)
+        if pair_weights is not None:
+            rows = rows * pair_weights.view(out.shape[0], top, 1)
+        acc = torch.zeros(out.shape, dtype=torch.float32)
+        for r in range(top):
+            acc += rows[:, r]
+        out.copy_(acc.to(out.dtype))
+
 
 def paged_attention(out, qkv, k_cache, v_cache, block_tables, q_start, seq_lens, H, KVH, D, page_size,
                     scale, window):

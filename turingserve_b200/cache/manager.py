@@ -3,6 +3,8 @@ per-request state slots.
 
 Runs of the schedule whose mixers want the same thing from the cache (same kv heads, head size
 and window) form a GROUP.  A group has its own pool ``[runs, 2, pages, kv_heads, page, head_dim]``
+(where a mixer's value rows are wider or narrower than its key rows: two tensors
+``[runs, pages, kv_heads, page, head_dim]`` and ``[runs, pages, kv_heads, page, value_dim]``)
 (the reference's single ``[L, 2, NB, KVH, 16, D]`` tensor, turingserve/engine/builder.py:76-80,
 is the one-group case), its own allocator and, per request, its own block table.  Pages go back
 to the group's free list when a request is released, and, in a windowed group, as soon as the
@@ -66,7 +68,9 @@ class CacheGroup:
         self.need = need
         self.runs = runs
         self.allocator = PageAllocator(num_pages)
-        self.pool: torch.Tensor | None = None
+        self.pool: torch.Tensor | None = None           # keys and values of one width
+        self.k_pool: torch.Tensor | None = None         # keys and values of two widths
+        self.v_pool: torch.Tensor | None = None
 
 
 class CacheManager:
@@ -85,7 +89,7 @@ class CacheManager:
         for r, n in enumerate(needs):
             if n.cache is None or n.cache_from is not None:
                 continue
-            key = (n.cache.num_kv_heads, n.cache.head_dim, n.cache.window)
+            key = (n.cache.num_kv_heads, n.cache.head_dim, n.cache.window, n.cache.v_dim)
             if key not in keys:
                 keys[key] = len(self.groups)
                 self.groups.append(CacheGroup(n.cache, [], num_pages))
@@ -99,13 +103,20 @@ class CacheManager:
                 if self._run_group[src] is None:
                     raise ValueError(f"run {r} reads the cache of run {src}, which has none")
                 a, b = needs[src].cache, n.cache
-                if b is not None and (a.num_kv_heads, a.head_dim) != (b.num_kv_heads, b.head_dim):
+                if b is not None and (a.num_kv_heads, a.head_dim, a.v_dim) != (b.num_kv_heads, b.head_dim, b.v_dim):
                     raise ValueError(f"run {r} cannot read run {src}'s cache: different kv shape")
         self.states: list[torch.Tensor | None] = [None] * len(needs)
         if device is not None:
             for grp in self.groups:
-                grp.pool = torch.zeros((len(grp.runs), 2, num_pages, grp.need.num_kv_heads, page_size,
-                                        grp.need.head_dim), dtype=dtype, device=device)
+                n = grp.need
+                if n.v_dim == n.head_dim:
+                    grp.pool = torch.zeros((len(grp.runs), 2, num_pages, n.num_kv_heads, page_size, n.head_dim),
+                                           dtype=dtype, device=device)
+                else:
+                    grp.k_pool = torch.zeros((len(grp.runs), num_pages, n.num_kv_heads, page_size, n.head_dim),
+                                             dtype=dtype, device=device)
+                    grp.v_pool = torch.zeros((len(grp.runs), num_pages, n.num_kv_heads, page_size, n.v_dim),
+                                             dtype=dtype, device=device)
             for r, n in enumerate(needs):
                 if n.state is not None:
                     self.states[r] = torch.zeros((max_requests + 1, *n.state.shape), dtype=n.state.dtype,
@@ -119,7 +130,7 @@ class CacheManager:
     def bytes_per_page(needs: list[RunNeeds], page_size: int, dtype: torch.dtype) -> int:
         """Bytes one page index costs across all groups (each group has ``num_pages`` pages)."""
         elem = torch.empty((), dtype=dtype).element_size()
-        return sum(2 * n.cache.num_kv_heads * n.cache.head_dim * page_size * elem
+        return sum(n.cache.num_kv_heads * (n.cache.head_dim + n.cache.v_dim) * page_size * elem
                    for n in needs if n.cache is not None and n.cache_from is None)
 
     # -- views --------------------------------------------------------------------------------------
@@ -134,6 +145,8 @@ class CacheManager:
         k = v = None
         if grp.pool is not None:
             k, v = grp.pool[i, 0], grp.pool[i, 1]
+        elif grp.k_pool is not None:
+            k, v = grp.k_pool[i], grp.v_pool[i]
         return CacheView(g, k, v, self.page_size, writable=n.cache_from is None)
 
     def views(self) -> list[CacheView | None]:

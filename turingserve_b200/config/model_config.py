@@ -67,6 +67,76 @@ class GatedMLPSpec:
     kind: str = "gated_mlp"
 
 
+@dataclass(frozen=True)
+class StreamRMSNormSpec:
+    """Root-mean-square norm of a residual stream that is kept in 32-bit whatever the engine's type:
+    x / sqrt(mean(x^2) + eps) * scale, all in 32-bit, rounded once."""
+
+    eps: float
+    weight_name: str = "weight"         # local tensor name of the scale ('' = the norm's prefix itself)
+    kind: str = "rmsnorm_stream"
+
+
+@dataclass(frozen=True)
+class LightningSpec:
+    """Linear attention with a matrix state per head and a fixed decay per head:
+    S_t = decay_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t with q, k, v = activation(projection); the heads'
+    outputs are normed together (RMS, learned scale), gated by sigmoid(gate projection) and projected."""
+
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    decays: tuple[float, ...]
+    norm_eps: float
+    activation: str = "silu"
+    kind: str = "lightning"
+
+
+@dataclass(frozen=True)
+class DiffAttentionSpec:
+    """Grouped-query softmax attention with two score maps a head over the same values
+    (differential attention): o = a1 - lam * a2, lam = exp(lq1.lk1) - exp(lq2.lk2) + ``diff``;
+    each head's o is divided by its root mean square and multiplied by 1 - ``diff``.  Queries and keys
+    are ``key_dim`` wide per map, values ``value_dim``; no position encoding."""
+
+    num_heads: int
+    num_kv_heads: int
+    key_dim: int
+    value_dim: int
+    scale: float
+    diff: float
+    norm_eps: float
+    qkv_bias: bool = True
+    out_bias: bool = False
+    kind: str = "diff_attention"
+
+
+@dataclass(frozen=True)
+class MLPSpec:
+    """Dense feed-forward without a gate: down(act(up(x)))."""
+
+    intermediate_size: int
+    activation: str = "gelu_tanh"       # gelu_tanh | relu2 | silu
+    kind: str = "mlp"
+
+
+@dataclass(frozen=True)
+class RoutedMLPSpec:
+    """Mixture of small feed-forwards down(act(up(.))) without biases: every token goes to the ``top_k``
+    experts with the largest router scores.  ``scoring``: sigmoid | softmax of the router logits (32-bit);
+    ``renormalize``: the chosen scores divided by their sum; ``weight_on``: "input" (the score multiplies
+    what the expert reads) or "output" (what it returns)."""
+
+    num_experts: int
+    top_k: int
+    intermediate_size: int
+    activation: str = "relu2"
+    scoring: str = "sigmoid"
+    renormalize: bool = False
+    weight_on: str = "input"
+    kind: str = "routed_mlp"
+
+
 class LayerSpec:
     """One decoder layer: the spec of each of its parts under a ROLE name, and the arrangement that
     wires them.
@@ -112,11 +182,15 @@ class LayerRun:
 
     ``layer`` indexes ``ModelConfig.layers`` (the weights to use).  ``cache_from`` is None when
     this run owns a cache of its own, or the index of an EARLIER entry of the schedule whose
-    cache this run reads without writing.
+    cache this run reads without writing.  Every run has its own cache and state: a layer that runs
+    twice keeps two.
     """
 
     layer: int
     cache_from: int | None = None
+    # the embedding rows of the step are added to the stream before this run (a model that runs a span of
+    # layers several times re-injects its input at the start of every later pass)
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)

@@ -17,7 +17,8 @@ from turingserve_b200.config.model_config import ModelConfig
 
 class LayerTensorNames:
     """Checkpoint prefix of every part of one layer, by the part's role in the layer (the role
-    names of its ``LayerSpec``); each prefix ends with '.' or is ''.  ``names["mixer"]`` or
+    names of its ``LayerSpec``); a prefix is put in front of the part's local tensor names, so it ends with
+    '.' or is '', or is a whole tensor name where the part's only tensor has the local name ''.  ``names["mixer"]`` or
     ``names.mixer``."""
 
     def __init__(self, **prefixes: str) -> None:
@@ -88,8 +89,10 @@ def get_architecture(name: str) -> Architecture:
 
 def architecture_of(config_json: dict) -> Architecture:
     archs = config_json.get("architectures")
+    if isinstance(config_json.get("architecture"), str) and not archs:
+        archs = [config_json["architecture"]]           # some families name themselves with one string
     if not archs or not isinstance(archs, (list, tuple)):
-        raise ValueError("config.json has no 'architectures' list; cannot choose a model class")
+        raise ValueError("config.json has no 'architectures' list (or 'architecture' name); cannot choose a model class")
     return get_architecture(archs[0])
 
 
@@ -116,3 +119,5 @@ def load_model_config(model_dir: str) -> ModelConfig:
 def _load_builtin() -> None:
     if "Qwen2ForCausalLM" not in _ARCHITECTURES:
         from turingserve_b200.models import qwen2  # noqa: F401  (registers itself)
+    if "Komirax" not in _ARCHITECTURES:
+        from turingserve_b200.models import komirax  # noqa: F401

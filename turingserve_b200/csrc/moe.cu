@@ -1,0 +1,280 @@
+// Routed feed-forward (mixture of experts): router with top-k choice, the grouping of (token, choice)
+// pairs by expert, products over the groups, and the sum of a token's choices.  Nothing here reads a
+// count back to the host: every launch is sized for the worst case and blocks without work leave, so the
+// chain can sit in a captured graph.
+//
+//   ts_router_topk     z = Wr x in 32-bit (one warp a token, fixed summation order), score = sigmoid(z) or
+//                      softmax(z); the `top` largest by z (ties: the lower index); weights = their scores,
+//                      optionally divided by their sum.
+//   ts_moe_align       pairs p = t * top + r sorted by expert: offsets[E + 1], order[P] (sorted place -> pair),
+//                      place[P] (pair -> sorted place), and the list of row tiles (expert, first row) the
+//                      grouped products walk.
+//   ts_grouped_linear  out[i, :] = act(a_i . W[e(i)]^T) for the sorted places i; a_i is row i of `x`, or, when
+//                      `order` is given, row order[i] / top of `x` times row_scale[order[i]] (rounded to the
+//                      storage type: the weighted input of an expert).  FFMA, 32-bit accumulation in
+//                      ascending k: a row's result does not depend on its tile-mates.
+//   ts_moe_combine     out[t, :] = sum over r (ascending) of (w[t, r] *) y[place[t * top + r], :], in 32-bit.
+#include "activations.cuh"
+#include "common.cuh"
+
+namespace {
+
+constexpr int GL_BM = 64, GL_BN = 64, GL_BK = 16, GL_PAD = 4;
+
+// ---------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+router_topk_kernel(int* __restrict__ idx_out, float* __restrict__ w_out, const T* __restrict__ x,
+                   const float* __restrict__ wr, int T_, int E, int K, int top, int softmax, int renorm) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + warp;
+  if (t >= T_) return;
+  float* z = smem + warp * E;
+  const T* xr = x + (size_t)t * K;
+  for (int e = 0; e < E; ++e) {
+    const float* wrow = wr + (size_t)e * K;
+    float acc = 0.f;
+    for (int k = lane; k < K; k += 32) acc = fmaf(to_f(xr[k]), wrow[k], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) z[e] = acc;
+  }
+  __syncwarp();
+  float zmax = -INFINITY, denom = 1.f;
+  if (softmax) {
+    for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, z[e]);
+    zmax = warp_max(zmax);
+    float d = 0.f;
+    for (int e = lane; e < E; e += 32) d += expf(z[e] - zmax);
+    denom = warp_sum(d);
+  }
+  float total = 0.f;
+  for (int r = 0; r < top; ++r) {
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = z[e];
+      if (v > best) {              // ascending e: the first of equal values stays
+        best = v;
+        arg = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ob > best || (ob == best && oa < arg)) {
+        best = ob;
+        arg = oa;
+      }
+    }
+    if (arg == 0x7fffffff) arg = 0;              // only when every score left is -inf or NaN
+    const float score = softmax ? expf(best - zmax) / denom : 1.f / (1.f + expf(-best));
+    total += score;
+    if (lane == 0) {
+      idx_out[(size_t)t * top + r] = arg;
+      w_out[(size_t)t * top + r] = score;
+      z[arg] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  if (renorm && lane == 0)
+    for (int r = 0; r < top; ++r) w_out[(size_t)t * top + r] /= total;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// One block.  tiles: [0] = number of row tiles, then (expert, first sorted row) pairs.
+__global__ void __launch_bounds__(1024)
+moe_align_kernel(const int* __restrict__ idx, int P, int E, int* __restrict__ offsets, int* __restrict__ order,
+                 int* __restrict__ place, int* __restrict__ tiles, int tile_rows) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ int sm_i[];
+  int* count = sm_i;          // [E]
+  int* cursor = sm_i + E;     // [E]
+  for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) atomicAdd(&count[min(max(idx[p], 0), E - 1)], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0, n = 0;
+    for (int e = 0; e < E; ++e) {
+      offsets[e] = at;
+      cursor[e] = at;
+      for (int r = 0; r < count[e]; r += tile_rows) {
+        tiles[1 + 2 * n] = e;
+        tiles[2 + 2 * n] = at + r;
+        ++n;
+      }
+      at += count[e];
+    }
+    offsets[E] = at;
+    tiles[0] = n;
+  }
+  __syncthreads();
+  // a pair's place inside its expert's group is whatever the cursor gives: a row's result does not depend
+  // on where in a tile it sits
+  for (int p = threadIdx.x; p < P; p += blockDim.x) {
+    const int at = atomicAdd(&cursor[min(max(idx[p], 0), E - 1)], 1);
+    order[at] = p;
+    place[p] = at;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+grouped_linear_kernel(TO* __restrict__ out, const TI* __restrict__ x, const TI* __restrict__ w,
+                      const int* __restrict__ order, const float* __restrict__ row_scale,
+                      const int* __restrict__ offsets, const int* __restrict__ tiles, int top, int N, int K, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if ((int)blockIdx.y >= tiles[0]) return;
+  const int e = tiles[1 + 2 * blockIdx.y], m0 = tiles[2 + 2 * blockIdx.y];
+  const int m_end = offsets[e + 1];
+  __shared__ __align__(16) float As[GL_BK][GL_BM + GL_PAD];
+  __shared__ __align__(16) float Ws[GL_BK][GL_BN + GL_PAD];
+  const int tid = threadIdx.x;
+  const int n0 = blockIdx.x * GL_BN;
+  const int lr = tid >> 2, lk = (tid & 3) * 4;
+  const int ty = tid >> 4, tx = tid & 15;
+  float acc[4][4] = {};
+
+  const int am = m0 + lr;
+  const TI* a_row = nullptr;
+  float a_scale = 1.f;
+  bool scaled = false;
+  if (am < m_end) {
+    if (order != nullptr) {
+      const int p = order[am];
+      a_row = x + (size_t)(p / top) * K;
+      if (row_scale != nullptr) {
+        a_scale = row_scale[p];
+        scaled = true;
+      }
+    } else {
+      a_row = x + (size_t)am * K;
+    }
+  }
+  const int wn = n0 + lr;
+  const TI* w_row = wn < N ? w + ((size_t)e * N + wn) * K : nullptr;
+
+  for (int k0 = 0; k0 < K; k0 += GL_BK) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int k = k0 + lk + i;
+      float a = (a_row != nullptr && k < K) ? to_f(a_row[k]) : 0.f;
+      if (scaled) a = round_to<TI>(a * a_scale);
+      As[lk + i][lr] = a;
+      Ws[lk + i][lr] = (w_row != nullptr && k < K) ? to_f(w_row[k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < GL_BK; ++k) {
+      const float4 a = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
+      const float4 b = *reinterpret_cast<const float4*>(&Ws[k][tx * 4]);
+      const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= m_end) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= N) continue;
+      out[(size_t)m * N + n] = from_f<TO>(ts_activate(acc[i][j], act));
+    }
+  }
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(T* __restrict__ out, const float* __restrict__ y, const int* __restrict__ place,
+                                   const float* __restrict__ pair_w, int top, int N) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  for (int n = threadIdx.x; n < N; n += blockDim.x) {
+    float acc = 0.f;
+    for (int r = 0; r < top; ++r) {
+      const size_t p = (size_t)t * top + r;
+      const float v = y[(size_t)place[p] * N + n];
+      acc += pair_w != nullptr ? pair_w[p] * v : v;
+    }
+    out[(size_t)t * N + n] = from_f<T>(acc);
+  }
+}
+
+}  // namespace
+
+TS_API int ts_moe_tile_rows() { return GL_BM; }
+
+// x: [T, K] in `dtype`; wr: [E, K] 32-bit.  idx_out / w_out: [T, top].
+TS_API int ts_router_topk(int* idx_out, float* w_out, const void* x, const float* wr, int T, int E, int K, int top,
+                          int softmax, int renorm, int dtype, void* stream) {
+  if (T <= 0) return 0;
+  if (E <= 0 || top <= 0 || top > E) TS_REFUSE(TS_ERR_SHAPE, "ts_router_topk: top %d of %d experts", top, E);
+  if (E > 2048) TS_REFUSE(TS_ERR_LIMIT, "ts_router_topk: %d experts (limit 2048)", E);
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t smem = sizeof(float) * 4 * E;
+  if (dtype == TS_F32)
+    ts_launch(router_topk_kernel<float>, dim3(ceil_div(T, 4)), dim3(128), smem, s, idx_out, w_out, (const float*)x, wr, T,
+              E, K, top, softmax, renorm);
+  else if (dtype == TS_BF16)
+    ts_launch(router_topk_kernel<bf16>, dim3(ceil_div(T, 4)), dim3(128), smem, s, idx_out, w_out, (const bf16*)x, wr, T,
+              E, K, top, softmax, renorm);
+  else
+    TS_REFUSE(TS_ERR_DTYPE, "ts_router_topk: dtype %d", dtype);
+  TS_LAUNCH_CHECK();
+}
+
+// tiles needs 1 + 2 * (ceil(P / tile_rows) + E) ints.
+TS_API int ts_moe_align(const int* idx, int P, int E, int* offsets, int* order, int* place, int* tiles, void* stream) {
+  if (P <= 0) return 0;
+  if (E > 4096) TS_REFUSE(TS_ERR_LIMIT, "ts_moe_align: %d experts (limit 4096)", E);
+  ts_launch(moe_align_kernel, dim3(1), dim3(1024), sizeof(int) * 2 * E, (cudaStream_t)stream, idx, P, E, offsets, order,
+            place, tiles, GL_BM);
+  TS_LAUNCH_CHECK();
+}
+
+// w: [E, N, K].  out: [P, N].  act: 0 none, 1 tanh-form GELU, 2 squared ReLU, 3 SiLU.
+TS_API int ts_grouped_linear(void* out, const void* x, const void* w, const int* order, const float* row_scale,
+                             const int* offsets, const int* tiles, int P, int E, int top, int N, int K, int act,
+                             int dtype, int out_dtype, void* stream) {
+  if (P <= 0 || N <= 0) return 0;
+  if (K <= 0) TS_REFUSE(TS_ERR_SHAPE, "ts_grouped_linear: K = %d", K);
+  cudaStream_t s = (cudaStream_t)stream;
+  dim3 grid(ceil_div(N, GL_BN), ceil_div(P, GL_BM) + E);
+  if (grid.y > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_grouped_linear: %d rows too many for one launch", P);
+#define TS_GLK(TI, TO)                                                                                           \
+  ts_launch(grouped_linear_kernel<TI, TO>, dim3(grid), dim3(256), 0, s, (TO*)out, (const TI*)x, (const TI*)w, order, \
+            row_scale, offsets, tiles, top, N, K, act)
+  if (dtype == TS_F32 && out_dtype == TS_F32) TS_GLK(float, float);
+  else if (dtype == TS_BF16 && out_dtype == TS_BF16) TS_GLK(bf16, bf16);
+  else if (dtype == TS_BF16 && out_dtype == TS_F32) TS_GLK(bf16, float);
+  else TS_REFUSE(TS_ERR_DTYPE, "ts_grouped_linear: dtype %d -> %d", dtype, out_dtype);
+#undef TS_GLK
+  TS_LAUNCH_CHECK();
+}
+
+// pair_w: [T * top] weights of the choices, or null (the weights went into the experts' inputs).
+TS_API int ts_moe_combine(void* out, const float* y, const int* place, const float* pair_w, int T, int top, int N, int dtype,
+                          void* stream) {
+  if (T <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == TS_F32)
+    ts_launch(moe_combine_kernel<float>, dim3(T), dim3(256), 0, s, (float*)out, y, place, pair_w, top, N);
+  else if (dtype == TS_BF16)
+    ts_launch(moe_combine_kernel<bf16>, dim3(T), dim3(256), 0, s, (bf16*)out, y, place, pair_w, top, N);
+  else
+    TS_REFUSE(TS_ERR_DTYPE, "ts_moe_combine: dtype %d", dtype);
+  TS_LAUNCH_CHECK();
+}

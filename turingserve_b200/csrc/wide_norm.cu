@@ -1,0 +1,114 @@
+// Row-wise kernels of models whose residual stream is kept in 32-bit whatever the engine's type:
+//   * the stream's own RMS norm, which first takes the pending branch outputs into the stream,
+//   * an RMS norm over a 32-bit row with a sigmoid gate from a second tensor (the output stage of a
+//     linear-attention mixer),
+//   * one-input activations (tanh-form GELU, squared ReLU, SiLU).
+// All arithmetic is 32-bit with one rounding to the output type.
+#include "activations.cuh"
+#include "common.cuh"
+
+namespace {
+
+// stream[row] (+)= add1[row] + add2[row];  out[row] = T(stream * rsqrt(mean(stream^2) + eps) * w)
+// first != 0: the stream row is not read (this call starts it).  add1 / add2 may be null.
+template <typename T, typename WT>
+__global__ void rmsnorm_wide_kernel(T* __restrict__ out, float* __restrict__ stream, const T* __restrict__ add1,
+                                    const T* __restrict__ add2, const WT* __restrict__ w, float eps, int hidden,
+                                    int first) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[32];
+  const size_t base = (size_t)blockIdx.x * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = first ? 0.f : stream[base + i];
+    if (add1 != nullptr) v += to_f(add1[base + i]);
+    if (add2 != nullptr) v += to_f(add2[base + i]);
+    stream[base + i] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  if (out == nullptr) return;
+  const float rstd = 1.f / sqrtf(ss / (float)hidden + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+    out[base + i] = from_f<T>(stream[base + i] * rstd * to_f(w[i]));
+}
+
+// out[row] = T(x * rsqrt(mean(x^2) + eps) * w * sigmoid(gate[row]));  x is 32-bit, the gate has its own row stride
+template <typename T, typename WT>
+__global__ void gated_rmsnorm_kernel(T* __restrict__ out, const float* __restrict__ x, const T* __restrict__ gate,
+                                     int gate_stride, const WT* __restrict__ w, float eps, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[32];
+  const float* xr = x + (size_t)blockIdx.x * n;
+  const T* gr = gate + (size_t)blockIdx.x * gate_stride;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) ss += xr[i] * xr[i];
+  ss = block_sum(ss, scratch);
+  const float rstd = 1.f / sqrtf(ss / (float)n + eps);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float g = 1.f / (1.f + expf(-to_f(gr[i])));
+    out[(size_t)blockIdx.x * n + i] = from_f<T>(xr[i] * rstd * to_f(w[i]) * g);
+  }
+}
+
+template <typename T>
+__global__ void activation_kernel(T* __restrict__ out, const T* __restrict__ x, size_t n, int kind) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = from_f<T>(ts_activate(to_f(x[i]), kind));
+}
+
+int threads_for(int n) { return n >= 2048 ? 512 : (n >= 512 ? 256 : 128); }
+
+}  // namespace
+
+TS_API int ts_rmsnorm_wide(void* out, float* stream, const void* add1, const void* add2, const void* w, float eps,
+                           int T, int hidden, int first, int dtype, int w_dtype, void* stream_) {
+  if (T <= 0) return 0;
+  if (first && add1 == nullptr) TS_REFUSE(TS_ERR_SHAPE, "ts_rmsnorm_wide: a stream starts from a tensor");
+  cudaStream_t s = (cudaStream_t)stream_;
+  const int th = threads_for(hidden);
+#define TS_WN(TT, WT)                                                                                         \
+  ts_launch(rmsnorm_wide_kernel<TT, WT>, dim3(T), dim3(th), 0, s, (TT*)out, stream, (const TT*)add1, (const TT*)add2, \
+            (const WT*)w, eps, hidden, first)
+  if (dtype == TS_F32 && w_dtype == TS_F32) TS_WN(float, float);
+  else if (dtype == TS_BF16 && w_dtype == TS_BF16) TS_WN(bf16, bf16);
+  else if (dtype == TS_BF16 && w_dtype == TS_F32) TS_WN(bf16, float);
+  else TS_REFUSE(TS_ERR_DTYPE, "ts_rmsnorm_wide: dtype %d with scale dtype %d", dtype, w_dtype);
+#undef TS_WN
+  TS_LAUNCH_CHECK();
+}
+
+TS_API int ts_gated_rmsnorm(void* out, const float* x, const void* gate, int gate_stride, const void* w, float eps,
+                            int T, int n, int dtype, int w_dtype, void* stream) {
+  if (T <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int th = threads_for(n);
+#define TS_GN(TT, WT)                                                                                          \
+  ts_launch(gated_rmsnorm_kernel<TT, WT>, dim3(T), dim3(th), 0, s, (TT*)out, x, (const TT*)gate, gate_stride, \
+            (const WT*)w, eps, n)
+  if (dtype == TS_F32 && w_dtype == TS_F32) TS_GN(float, float);
+  else if (dtype == TS_BF16 && w_dtype == TS_BF16) TS_GN(bf16, bf16);
+  else if (dtype == TS_BF16 && w_dtype == TS_F32) TS_GN(bf16, float);
+  else TS_REFUSE(TS_ERR_DTYPE, "ts_gated_rmsnorm: dtype %d with scale dtype %d", dtype, w_dtype);
+#undef TS_GN
+  TS_LAUNCH_CHECK();
+}
+
+// kind: 1 tanh-form GELU, 2 squared ReLU, 3 SiLU.  out may be x.
+TS_API int ts_activation(void* out, const void* x, long long n, int kind, int dtype, void* stream) {
+  if (n <= 0) return 0;
+  if (kind < 1 || kind > 3) TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_activation: kind %d", kind);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int blocks = (int)((n + 1023) / 1024 < 148 * 8 ? (n + 1023) / 1024 : 148 * 8);
+  if (dtype == TS_F32)
+    ts_launch(activation_kernel<float>, dim3(blocks), dim3(256), 0, s, (float*)out, (const float*)x, (size_t)n, kind);
+  else if (dtype == TS_BF16)
+    ts_launch(activation_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (bf16*)out, (const bf16*)x, (size_t)n, kind);
+  else
+    TS_REFUSE(TS_ERR_DTYPE, "ts_activation: dtype %d", dtype);
+  TS_LAUNCH_CHECK();
+}

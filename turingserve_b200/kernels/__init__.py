@@ -68,7 +68,7 @@ class LazyProduct:
 class CudaOps:
     """ctypes front of ``libturingserve_b200.so``."""
 
-    ABI = 8
+    ABI = 9
     UNSUPPORTED = -4            # a kernel's refusal of a shape or layout another kernel takes
 
     def __init__(self, lib_path: str) -> None:
@@ -108,11 +108,23 @@ class CudaOps:
             "ts_decode_step": [P, I, I, P],
             "ts_decode_step_encode_map": [P, P, I, I],
             "ts_poke_status": [I, I, P],
+            "ts_rmsnorm_wide": [P, P, P, P, P, F, I, I, I, I, I, P],
+            "ts_gated_rmsnorm": [P, P, P, I, P, F, I, I, I, I, P],
+            "ts_activation": [P, P, ctypes.c_longlong, I, I, P],
+            "ts_lightning": [P, P, I, P, P, P, P, I, I, I, I, I, P],
+            "ts_kv_write_pair": [P, I, I, I, P, P, P, I, I, I, I, I, I, P],
+            "ts_attention_diff": [P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, F, F, I, P],
+            "ts_router_topk": [P, P, P, P, I, I, I, I, I, I, I, P],
+            "ts_moe_align": [P, I, I, P, P, P, P, P],
+            "ts_grouped_linear": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
+            "ts_moe_combine": [P, P, P, P, I, I, I, I, P],
         }
         for name, args in sigs.items():
             fn = getattr(self.lib, name)
             fn.argtypes = args
             fn.restype = c_int
+        self.lib.ts_moe_tile_rows.argtypes = []
+        self.lib.ts_moe_tile_rows.restype = c_int
         self.lib.ts_attention_decode_supported.argtypes = [I, I, I, I]
         self.lib.ts_attention_decode_supported.restype = c_int
         self.lib.ts_attention_decode_tma_supported.argtypes = [I, I, I, I, I]
@@ -518,6 +530,101 @@ class CudaOps:
         self._check(self.lib.ts_linear_simt(_ptr(out), _ptr(x), _ptr(w), _ptr(bias), _ptr(rows), M, N, K,
                                             _code(x.dtype), _code(out.dtype), self._stream()), "linear")
         return out
+
+    # -- a residual stream in 32-bit ---------------------------------------------------------------------
+    def rmsnorm_stream(self, out, stream, add1, add2, weight, eps: float, first: bool = False) -> None:
+        """stream (float32 [T, h]) += add1 + add2 (either may be None; ``first``: the stream is started
+        from them instead); out = stream / sqrt(mean(stream^2) + eps) * weight, 32-bit, rounded once.
+        ``out`` None: only the sum."""
+        T, h = stream.shape
+        add1, add2 = self.materialize(add1), self.materialize(add2)
+        dt = add1.dtype if add1 is not None else (add2.dtype if add2 is not None else out.dtype)
+        self._check(self.lib.ts_rmsnorm_wide(_ptr(out), _ptr(stream), _ptr(add1), _ptr(add2), _ptr(weight), float(eps),
+                                             T, h, 1 if first else 0, _code(dt), _code(weight.dtype), self._stream()),
+                    "rmsnorm_stream")
+
+    def gated_rmsnorm(self, out, x, gate, weight, eps: float) -> None:
+        """out = x / sqrt(mean(x^2) + eps) * weight * sigmoid(gate), x float32 [T, n]; ``gate`` [T, n] in
+        out's type, possibly a column slice of a wider tensor."""
+        T, n = x.shape
+        if gate.stride(1) != 1:
+            raise ValueError("gated_rmsnorm: the gate's rows must be contiguous")
+        self._check(self.lib.ts_gated_rmsnorm(_ptr(out), _ptr(x), _ptr(gate), gate.stride(0), _ptr(weight), float(eps), T,
+                                              n, _code(out.dtype), _code(weight.dtype), self._stream()), "gated_rmsnorm")
+
+    ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "relu2": 2, "silu": 3}
+
+    def activation(self, out, x, kind: str) -> None:
+        """out = act(x) elementwise (32-bit arithmetic, one rounding); out may be x."""
+        self._check(self.lib.ts_activation(_ptr(out), _ptr(x), x.numel(), self.ACTIVATIONS[kind], _code(x.dtype),
+                                           self._stream()), "activation")
+
+    # -- linear attention with a decaying matrix state ----------------------------------------------------
+    def lightning(self, out, proj, state, decay, step, H: int, D: int, V: int) -> None:
+        """out (float32 [T, H V]): per head o_t = S_t^T q_t with S_t = decay_h S_(t-1) + k_t v_t^T, where
+        q, k, v = silu of the columns [0, HD), [HD, 2HD), [2HD, 2HD + HV) of ``proj``; ``state``
+        (float32 [slots, H, D, V]) is read and left updated at each request's slot."""
+        self._check(self.lib.ts_lightning(_ptr(out), _ptr(proj), proj.stride(0), _ptr(state), _ptr(decay),
+                                          _ptr(step.q_start), _ptr(step.state_slots), step.num_requests, H, D, V,
+                                          _code(proj.dtype), self._stream()), "lightning")
+
+    # -- attention with two score maps a head --------------------------------------------------------------
+    def kv_write_pair(self, proj, k_off: int, v_off: int, k_cache, v_cache, slots, KVH: int, DK: int, DV: int,
+                      page_size: int) -> None:
+        """The step's new key rows (columns k_off.. of ``proj``, KVH x DK) and value rows (v_off.., KVH x DV)
+        into their cache slots; a slot of -1 writes nothing."""
+        self._check(self.lib.ts_kv_write_pair(_ptr(proj), proj.stride(0), k_off, v_off, _ptr(k_cache), _ptr(v_cache),
+                                              _ptr(slots), proj.shape[0], KVH, DK, DV, page_size, _code(proj.dtype),
+                                              self._stream()), "kv_write_pair")
+
+    def attention_diff(self, out, proj, k_cache, v_cache, block_tables, step, H: int, KVH: int, D: int, V: int,
+                       page_size: int, scale: float, lam: float, eps: float, out_scale: float) -> None:
+        """out [T, H V] = out_scale * rmsnorm_head(a1 - lam a2): two causal softmax maps a head (queries in
+        the first H 2D columns of ``proj`` as [map 1 | map 2] per head, cached key rows 2D wide) over the
+        same cached values."""
+        self._check(self.lib.ts_attention_diff(
+            _ptr(out), _ptr(proj), proj.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(step.q_start),
+            _ptr(step.seq_lens), step.num_requests, block_tables.shape[1], step.max_q_len, H, KVH, D, V, page_size,
+            float(scale), float(lam), float(eps), float(out_scale), _code(proj.dtype), self._stream()), "attention_diff")
+
+    # -- routed feed-forward ---------------------------------------------------------------------------------
+    def router_topk(self, idx, weights, x, w_router, softmax: bool, renormalize: bool) -> None:
+        """idx (int32 [T, top]), weights (float32 [T, top]): the ``top`` experts with the largest router
+        logits w_router (float32 [E, K]) . x, and their scores (sigmoid, or softmax over all experts)."""
+        T, top = idx.shape
+        E, K = w_router.shape
+        self._check(self.lib.ts_router_topk(_ptr(idx), _ptr(weights), _ptr(x), _ptr(w_router), T, E, K, top,
+                                            1 if softmax else 0, 1 if renormalize else 0, _code(x.dtype), self._stream()),
+                    "router_topk")
+
+    def moe_align(self, idx, E: int):
+        """Sorts the (token, choice) pairs of ``idx`` by expert on the device.  Returns (offsets [E + 1],
+        order [P], place [P], tiles): work buffers of this object, valid until the next call."""
+        P = idx.numel()
+        dev = idx.device
+        rows = self.lib.ts_moe_tile_rows()
+        offsets = self._buffer("moe_offsets", E + 1, torch.int32, dev, floor=1024)
+        order = self._buffer("moe_order", P, torch.int32, dev, floor=1 << 14)
+        place = self._buffer("moe_place", P, torch.int32, dev, floor=1 << 14)
+        tiles = self._buffer("moe_tiles", 1 + 2 * (-(-P // rows) + E), torch.int32, dev, floor=1 << 12)
+        self._check(self.lib.ts_moe_align(_ptr(idx), P, E, _ptr(offsets), _ptr(order), _ptr(place), _ptr(tiles),
+                                          self._stream()), "moe_align")
+        return offsets, order, place, tiles
+
+    def grouped_linear(self, out, x, w, order, row_scale, offsets, tiles, top: int, act: str = "none") -> None:
+        """out[i] = act(a_i . w[e_i]^T) for the P sorted places i (``w`` [E, N, K]); a_i = x[i], or with
+        ``order``: x[order[i] // top] (times row_scale[order[i]], rounded to x's type)."""
+        P, N = out.shape
+        E, _, K = w.shape
+        self._check(self.lib.ts_grouped_linear(_ptr(out), _ptr(x), _ptr(w), _ptr(order), _ptr(row_scale), _ptr(offsets),
+                                               _ptr(tiles), P, E, top, N, K, self.ACTIVATIONS[act], _code(x.dtype),
+                                               _code(out.dtype), self._stream()), "grouped_linear")
+
+    def moe_combine(self, out, y, place, pair_weights, top: int) -> None:
+        """out[t] = sum over a token's choices r of (pair_weights[t, r] *) y[place[t top + r]] (y float32)."""
+        T, N = out.shape
+        self._check(self.lib.ts_moe_combine(_ptr(out), _ptr(y), _ptr(place), _ptr(pair_weights), T, top, N,
+                                            _code(out.dtype), self._stream()), "moe_combine")
 
     PAIR_PLAIN, PAIR_GATED = 0, 1
     # The many-row products whose epilogue saves a kernel (gate/up with the activation, q/k/v with rotation and

@@ -46,11 +46,18 @@ class ParamSpec:
 @dataclass(frozen=True)
 class CacheNeed:
     """What a mixer wants from the paged cache: keys and values of ``num_kv_heads`` x ``head_dim``
-    per token; ``window`` None keeps every token, an integer keeps the last ``window`` of them."""
+    per token; ``window`` None keeps every token, an integer keeps the last ``window`` of them.
+    ``value_dim``: the width of a value row where it differs from a key row's ``head_dim`` (the
+    group's keys and values are then two tensors instead of one pool)."""
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    value_dim: int | None = None
+
+    @property
+    def v_dim(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
 
 @dataclass(frozen=True)
@@ -133,7 +140,8 @@ def _load_builtin() -> None:
     global _loaded
     if not _loaded:
         _loaded = True
-        from turingserve_b200.parts import attention, block, gated_mlp, rmsnorm, rotary  # noqa: F401
+        from turingserve_b200.parts import (  # noqa: F401
+            attention, block, diff_attention, gated_mlp, lightning, mlp, rmsnorm, rotary, routed_mlp)
 
 
 def build_block(layer_spec: Any, ctx: BuildContext):

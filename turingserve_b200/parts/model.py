@@ -64,10 +64,13 @@ class DecoderModel:
 
         ``cache_views[r]`` / ``states[r]``: the cache view and the state tensor of run r (or None).
         """
-        h = self.embed(step)
+        h = h0 = self.embed(step)
         residual = None
         for r, run in enumerate(self.cfg.schedule):
-            h, residual = self.blocks[run.layer].forward(h, residual, step, cache_views[r], states[r])
+            if run.add_embedding:
+                h, residual = self.blocks[run.layer].forward(h, residual, step, cache_views[r], states[r], inject=h0)
+            else:
+                h, residual = self.blocks[run.layer].forward(h, residual, step, cache_views[r], states[r])
         return self.final_norm.forward(h, residual)
 
     def embed(self, step) -> torch.Tensor:

@@ -33,4 +33,34 @@ class RMSNorm(Norm):
         return out
 
 
+class StreamRMSNorm(Norm):
+    """The norm of a residual stream kept in 32-bit whatever the engine's type: ``forward(x, stream)``
+    first adds the pending branch output ``x`` (and ``extra``, when given) to ``stream`` in place, then
+    returns stream / sqrt(mean(stream^2) + eps) * weight in the engine's type (32-bit arithmetic, one
+    rounding).  ``first``: ``stream`` is started from ``x`` instead of added to.  The spec's
+    ``weight_name`` is the scale's local tensor name ('' where the checkpoint names the scale by the
+    norm's own prefix)."""
+
+    def __init__(self, spec, ctx: BuildContext) -> None:
+        self.eps = float(spec.eps)
+        self.size = ctx.hidden_size
+        self.dtype = ctx.dtype
+        self.weight_name = str(getattr(spec, "weight_name", "weight"))
+        self.weight: torch.Tensor | None = None
+
+    def parameters(self) -> dict[str, ParamSpec]:
+        return {self.weight_name: ParamSpec((self.size,), compute_dtype=False, init="ones")}
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        self.weight = tensors[self.weight_name].contiguous()
+
+    def forward(self, x, residual: torch.Tensor | None = None, extra=None, first: bool = False) -> torch.Tensor:
+        if residual is None:
+            raise ValueError("the stream norm needs the 32-bit stream it adds to")
+        out = torch.empty(residual.shape, dtype=self.dtype, device=residual.device)
+        kernels.ops().rmsnorm_stream(out, residual, x, extra, self.weight, self.eps, first)
+        return out
+
+
 register("norm", "rmsnorm", RMSNorm)
+register("norm", "rmsnorm_stream", StreamRMSNorm)
