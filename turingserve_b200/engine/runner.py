@@ -210,7 +210,10 @@ class _StepGraph:
             s = torch.cuda.Stream()
             s.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(s):
-                r.forward(step)
+                # the warm-up run is a run too: a mixer that carries state from step to step would take this
+                # step's tokens into it twice (cache writes are the same bytes twice), so the warm-up's rows all
+                # point at the null state slot
+                r.forward(dataclasses.replace(step, state_slots=torch.full_like(step.state_slots, r.cache.null_slot)))
             torch.cuda.current_stream().wait_stream(s)
             graph = torch.cuda.CUDAGraph()
             before = getattr(ops, "launches", 0)
