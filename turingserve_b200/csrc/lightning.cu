@@ -6,15 +6,20 @@
 // would round it; everything from there on (products with the state, decay, the state itself, the
 // output) is 32-bit.  Output: 32-bit rows [T, H V] (a norm over all heads follows in another kernel).
 //
-// ts_lightning runs the tokens of a step in order: one block per (head, request); thread j owns column
-// j of the state.  A request's only token (decoding) updates the state in place in global memory; a
-// portion keeps the state in shared memory over its tokens, which arrive in groups of LT_GROUP rows
-// staged in shared memory.
+// ts_lightning runs the tokens of a step in order, exactly as written above, for single tokens and for
+// portions alike, so how a prompt is cut never changes a bit.  The columns of S are independent of one
+// another: one block owns LT_COLS columns of one (head, request) and keeps them in REGISTERS over all tokens
+// of the step: thread (part, col) holds rows part * LT_ROWS .. of column col.  Tokens arrive in groups of
+// LT_GROUP rows staged (and activated) in shared memory; a group's partial outputs of the row parts are
+// summed through shared memory, in part order.  Per token a thread does 3 * LT_ROWS 32-bit operations on
+// registers with two broadcast loads from shared memory.
 #include "common.cuh"
 
 namespace {
 
-constexpr int LT_GROUP = 16;
+constexpr int LT_GROUP = 16;     // tokens staged at a time
+constexpr int LT_COLS = 32;      // state columns per block (one lane each)
+constexpr int LT_ROWS = 32;      // state rows per thread (registers)
 
 template <typename T> __device__ __forceinline__ float act_silu(float z) { return round_to<T>(z / (1.f + expf(-z))); }
 
@@ -22,58 +27,79 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 lightning_kernel(float* __restrict__ out, const T* __restrict__ proj, int proj_stride, float* __restrict__ state,
                  const float* __restrict__ decay, const int* __restrict__ q_start, const int* __restrict__ slots,
-                 int H, int D, int V, int state_in_smem) {
+                 int H, int D, int V, int parts) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float smem[];
-  const int h = blockIdx.x, b = blockIdx.y;
+  extern __shared__ __align__(16) float smem[];
+  const int h = blockIdx.y, b = blockIdx.z;
   const int t0 = q_start[b], n = q_start[b + 1] - t0;
   if (n <= 0) return;
+  const int Dp = parts * LT_ROWS;                          // D rounded up: rows beyond D hold zero keys and queries
+  const int col = threadIdx.x & (LT_COLS - 1), part = threadIdx.x / LT_COLS;
+  const int j = blockIdx.x * LT_COLS + col;
+  const bool live = j < V;
   const float lam = decay[h];
   float* S = state + ((size_t)slots[b] * H + h) * D * V;
-  float* q_s = smem;                       // [LT_GROUP][D]
-  float* k_s = q_s + LT_GROUP * D;         // [LT_GROUP][D]
-  float* v_s = k_s + LT_GROUP * D;         // [LT_GROUP][V]
-  float* S_s = v_s + LT_GROUP * V;         // [D][V] when state_in_smem
-  const bool staged = state_in_smem && n > 1;
-  if (staged) {
-    for (int i = threadIdx.x; i < D * V; i += blockDim.x) S_s[i] = S[i];
+  float* q_s = smem;                                       // [LT_GROUP][Dp]
+  float* k_s = q_s + LT_GROUP * Dp;                        // [LT_GROUP][Dp]
+  float* v_s = k_s + LT_GROUP * Dp;                        // [LT_GROUP][LT_COLS]
+  float* o_s = v_s + LT_GROUP * LT_COLS;                   // [LT_GROUP][parts][LT_COLS]
+
+  float s[LT_ROWS];
+#pragma unroll
+  for (int i = 0; i < LT_ROWS; ++i) {
+    const int d = part * LT_ROWS + i;
+    s[i] = (live && d < D) ? S[(size_t)d * V + j] : 0.f;
   }
-  float* St = staged ? S_s : S;
   const int q_off = h * D, k_off = H * D + h * D, v_off = 2 * H * D + h * V;
   for (int g0 = 0; g0 < n; g0 += LT_GROUP) {
     const int gn = min(LT_GROUP, n - g0);
-    __syncthreads();
-    for (int i = threadIdx.x; i < gn * D; i += blockDim.x) {
-      const int r = i / D, d = i % D;
+    __syncthreads();                                       // the group before has been summed and stored
+    for (int i = threadIdx.x; i < gn * Dp; i += blockDim.x) {
+      const int r = i / Dp, d = i % Dp;
       const T* row = proj + (size_t)(t0 + g0 + r) * proj_stride;
-      q_s[i] = act_silu<T>(to_f(row[q_off + d]));
-      k_s[i] = act_silu<T>(to_f(row[k_off + d]));
+      q_s[i] = d < D ? act_silu<T>(to_f(row[q_off + d])) : 0.f;
+      k_s[i] = d < D ? act_silu<T>(to_f(row[k_off + d])) : 0.f;
     }
-    for (int i = threadIdx.x; i < gn * V; i += blockDim.x) {
-      const int r = i / V, d = i % V;
-      v_s[i] = act_silu<T>(to_f(proj[(size_t)(t0 + g0 + r) * proj_stride + v_off + d]));
+    for (int i = threadIdx.x; i < gn * LT_COLS; i += blockDim.x) {
+      const int r = i / LT_COLS, c = i % LT_COLS;
+      const int jj = blockIdx.x * LT_COLS + c;
+      v_s[i] = jj < V ? act_silu<T>(to_f(proj[(size_t)(t0 + g0 + r) * proj_stride + v_off + jj])) : 0.f;
     }
     __syncthreads();
-    for (int j = threadIdx.x; j < V; j += blockDim.x) {
-      for (int r = 0; r < gn; ++r) {
-        const float vj = v_s[r * V + j];
-        const float* qr = q_s + r * D;
-        const float* kr = k_s + r * D;
-        float o = 0.f;
-#pragma unroll 4
-        for (int i = 0; i < D; ++i) {
-          const float s = fmaf(lam, St[i * V + j], kr[i] * vj);
-          St[i * V + j] = s;
-          o = fmaf(s, qr[i], o);
-        }
-        out[(size_t)(t0 + g0 + r) * H * V + h * V + j] = o;
+    for (int r = 0; r < gn; ++r) {
+      const float vj = v_s[r * LT_COLS + col];
+      const float4* qr = reinterpret_cast<const float4*>(q_s + r * Dp + part * LT_ROWS);
+      const float4* kr = reinterpret_cast<const float4*>(k_s + r * Dp + part * LT_ROWS);
+      float o = 0.f;
+#pragma unroll
+      for (int i = 0; i < LT_ROWS / 4; ++i) {
+        const float4 k4 = kr[i], q4 = qr[i];
+        s[4 * i + 0] = fmaf(lam, s[4 * i + 0], k4.x * vj);
+        o = fmaf(s[4 * i + 0], q4.x, o);
+        s[4 * i + 1] = fmaf(lam, s[4 * i + 1], k4.y * vj);
+        o = fmaf(s[4 * i + 1], q4.y, o);
+        s[4 * i + 2] = fmaf(lam, s[4 * i + 2], k4.z * vj);
+        o = fmaf(s[4 * i + 2], q4.z, o);
+        s[4 * i + 3] = fmaf(lam, s[4 * i + 3], k4.w * vj);
+        o = fmaf(s[4 * i + 3], q4.w, o);
       }
+      o_s[(r * parts + part) * LT_COLS + col] = o;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < gn * LT_COLS; i += blockDim.x) {
+      const int r = i / LT_COLS, c = i % LT_COLS;
+      const int jj = blockIdx.x * LT_COLS + c;
+      if (jj >= V) continue;
+      float o = 0.f;
+      for (int p = 0; p < parts; ++p) o += o_s[(r * parts + p) * LT_COLS + c];
+      out[(size_t)(t0 + g0 + r) * H * V + h * V + jj] = o;
     }
   }
-  if (staged) {
-    __syncthreads();
-    for (int i = threadIdx.x; i < D * V; i += blockDim.x) S[i] = S_s[i];
+#pragma unroll
+  for (int i = 0; i < LT_ROWS; ++i) {
+    const int d = part * LT_ROWS + i;
+    if (live && d < D) S[(size_t)d * V + j] = s[i];
   }
 }
 
@@ -85,17 +111,12 @@ TS_API int ts_lightning(float* out, const void* proj, int proj_stride, float* st
                         const int* q_start, const int* slots, int B, int H, int D, int V, int dtype, void* stream) {
   if (B <= 0) return 0;
   if (H <= 0 || D <= 0 || V <= 0) TS_REFUSE(TS_ERR_SHAPE, "ts_lightning: %d heads of %d x %d", H, D, V);
-  if (B > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_lightning: %d requests per launch", B);
+  const int parts = ceil_div(D, LT_ROWS);
+  if (parts * LT_COLS > 256) TS_REFUSE(TS_ERR_LIMIT, "ts_lightning: keys of %d (limit %d)", D, 256 / LT_COLS * LT_ROWS);
+  if (B > 65535 || H > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_lightning: %d requests / %d heads per launch", B, H);
   cudaStream_t s = (cudaStream_t)stream;
-  const size_t group = sizeof(float) * LT_GROUP * (2 * (size_t)D + V);
-  size_t smem = group + sizeof(float) * (size_t)D * V;
-  int in_smem = 1;
-  if (smem > 200 * 1024) {          // a state too large for shared memory stays in global memory (and in L2)
-    smem = group;
-    in_smem = 0;
-  }
-  if (group > 200 * 1024) TS_REFUSE(TS_ERR_LIMIT, "ts_lightning: heads of %d x %d are too wide", D, V);
-  const int threads = V >= 256 ? 256 : (V + 31) / 32 * 32;
+  const size_t smem = sizeof(float) * LT_GROUP * ((size_t)2 * parts * LT_ROWS + LT_COLS + (size_t)parts * LT_COLS);
+  dim3 grid(ceil_div(V, LT_COLS), H, B);
 #define TS_LT(TT)                                                                                                   \
   do {                                                                                                              \
     static size_t configured = 0;                                                                                   \
@@ -104,8 +125,8 @@ TS_API int ts_lightning(float* out, const void* proj, int proj_stride, float* st
       if (e != cudaSuccess) TS_REFUSE((int)e, "ts_lightning: shared memory %zu: %s", smem, cudaGetErrorString(e)); \
       configured = smem;                                                                                            \
     }                                                                                                               \
-    ts_launch(lightning_kernel<TT>, dim3(H, B), dim3(threads), smem, s, out, (const TT*)proj, proj_stride, state, \
-              decay, q_start, slots, H, D, V, in_smem);                                                             \
+    ts_launch(lightning_kernel<TT>, dim3(grid), dim3(parts * LT_COLS), smem, s, out, (const TT*)proj, proj_stride, \
+              state, decay, q_start, slots, H, D, V, parts);                                                        \
   } while (0)
   if (dtype == TS_F32) TS_LT(float);
   else if (dtype == TS_BF16) TS_LT(bf16);

@@ -11,11 +11,13 @@
 //                      grouped products walk.
 //   ts_grouped_linear  out[i, :] = act(a_i . W[e(i)]^T) for the sorted places i; a_i is row i of `x`, or, when
 //                      `order` is given, row order[i] / top of `x` times row_scale[order[i]] (rounded to the
-//                      storage type: the weighted input of an expert).  FFMA, 32-bit accumulation in
-//                      ascending k: a row's result does not depend on its tile-mates.
+//                      storage type: the weighted input of an expert).  32-bit accumulation in ascending k
+//                      (FFMA; tensor cores for bfloat16 with K a multiple of 8): a row's result does not
+//                      depend on its tile-mates.
 //   ts_moe_combine     out[t, :] = sum over r (ascending) of (w[t, r] *) y[place[t * top + r], :], in 32-bit.
 #include "activations.cuh"
 #include "common.cuh"
+#include "mma_utils.cuh"
 
 namespace {
 
@@ -196,6 +198,120 @@ grouped_linear_kernel(TO* __restrict__ out, const TI* __restrict__ x, const TI* 
   }
 }
 
+
+// The same product on the tensor cores (bfloat16 operands, 32-bit accumulation): tiles of 64 sorted rows x 64
+// output columns, k in steps of 64 through a 3-stage cp.async pipeline into XOR-swizzled shared memory; each
+// of the 4 warps owns 16 rows.  Where the rows are weighted, the staged tile of inputs is multiplied in shared
+// memory (32-bit, rounded to bfloat16) before the products read it.  K must be a multiple of 8.
+constexpr int GM_BM = 64, GM_BN = 64, GM_BK = 64, GM_STAGES = 3, GM_WARPS = 4;
+static_assert(GM_BM == GL_BM, "both grouped kernels walk the same row tiles");
+
+template <typename TO>
+__global__ void __launch_bounds__(GM_WARPS * 32)
+grouped_linear_mma_kernel(TO* __restrict__ out, const bf16* __restrict__ x, const bf16* __restrict__ w,
+                          const int* __restrict__ order, const float* __restrict__ row_scale,
+                          const int* __restrict__ offsets, const int* __restrict__ tiles, int top, int N, int K, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if ((int)blockIdx.y >= tiles[0]) return;
+  const int e = tiles[1 + 2 * blockIdx.y], m0 = tiles[2 + 2 * blockIdx.y];
+  const int m_end = offsets[e + 1];
+  extern __shared__ __align__(128) unsigned char gsm[];
+  constexpr int A_STAGE = GM_BM * GM_BK * 2, B_STAGE = GM_BN * GM_BK * 2;
+  unsigned char* a_s = gsm;
+  unsigned char* b_s = gsm + GM_STAGES * A_STAGE;
+  __shared__ const bf16* a_rows[GM_BM];
+  __shared__ float a_scales[GM_BM];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int n0 = blockIdx.x * GM_BN;
+  if (tid < GM_BM) {
+    const int am = m0 + tid;
+    const bf16* row = nullptr;
+    float sc = 1.f;
+    if (am < m_end) {
+      if (order != nullptr) {
+        const int p = order[am];
+        row = x + (size_t)(p / top) * K;
+        if (row_scale != nullptr) sc = row_scale[p];
+      } else {
+        row = x + (size_t)am * K;
+      }
+    }
+    a_rows[tid] = row;
+    a_scales[tid] = sc;
+  }
+  __syncthreads();
+  const bf16* wb = w + (size_t)e * N * K;
+  const int k_tiles = (K + GM_BK - 1) / GM_BK;
+
+  auto load_tile = [&](int kt, int stage) {
+    const int k0 = kt * GM_BK;
+    for (int idx = tid; idx < GM_BM * 8; idx += GM_WARPS * 32) {
+      const int r = idx >> 3, c = idx & 7;
+      const bool ok = a_rows[r] != nullptr && k0 + c * 8 < K;
+      cp_async_16(a_s + stage * A_STAGE + swz<GM_BK>(r, c), ok ? a_rows[r] + k0 + c * 8 : x, ok);
+    }
+    for (int idx = tid; idx < GM_BN * 8; idx += GM_WARPS * 32) {
+      const int r = idx >> 3, c = idx & 7;
+      const bool ok = n0 + r < N && k0 + c * 8 < K;
+      cp_async_16(b_s + stage * B_STAGE + swz<GM_BK>(r, c), ok ? wb + (size_t)(n0 + r) * K + k0 + c * 8 : w, ok);
+    }
+  };
+
+  float acc[GM_BN / 8][4];
+#pragma unroll
+  for (int i = 0; i < GM_BN / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+#pragma unroll
+  for (int s_ = 0; s_ < GM_STAGES - 1; ++s_) {
+    if (s_ < k_tiles) load_tile(s_, s_);
+    cp_async_commit();
+  }
+  for (int kt = 0; kt < k_tiles; ++kt) {
+    if (kt + GM_STAGES - 1 < k_tiles) load_tile(kt + GM_STAGES - 1, (kt + GM_STAGES - 1) % GM_STAGES);
+    cp_async_commit();
+    cp_async_wait<GM_STAGES - 1>();
+    __syncthreads();
+    unsigned char* as_ = a_s + (kt % GM_STAGES) * A_STAGE;
+    const unsigned char* bs_ = b_s + (kt % GM_STAGES) * B_STAGE;
+    if (row_scale != nullptr) {
+      for (int idx = tid; idx < GM_BM * 8; idx += GM_WARPS * 32) {
+        const int r = idx >> 3, c = idx & 7;
+        const float sc = a_scales[r];
+        __nv_bfloat162* v = reinterpret_cast<__nv_bfloat162*>(as_ + swz<GM_BK>(r, c));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(v[i]);
+          v[i] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+        }
+      }
+      __syncthreads();
+    }
+#pragma unroll
+    for (int ks = 0; ks < GM_BK / 16; ++ks) {
+      const int mat = lane >> 3, r = lane & 7;
+      unsigned a[4];
+      ldmatrix_x4(a[0], a[1], a[2], a[3], as_ + swz<GM_BK>(warp * 16 + (mat & 1) * 8 + r, ks * 2 + (mat >> 1)));
+#pragma unroll
+      for (int np = 0; np < GM_BN / 16; ++np) {
+        unsigned b0, b1, b2, b3;
+        ldmatrix_x4(b0, b1, b2, b3, bs_ + swz<GM_BK>(np * 16 + (mat >> 1) * 8 + r, ks * 2 + (mat & 1)));
+        mma_bf16(acc[2 * np], a, b0, b1);
+        mma_bf16(acc[2 * np + 1], a, b2, b3);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int nt = 0; nt < GM_BN / 8; ++nt)
+#pragma unroll
+    for (int e_ = 0; e_ < 4; ++e_) {
+      const int m = m0 + warp * 16 + (lane >> 2) + 8 * (e_ >> 1);
+      const int n = n0 + nt * 8 + (lane & 3) * 2 + (e_ & 1);
+      if (m < m_end && n < N) out[(size_t)m * N + n] = from_f<TO>(ts_activate(acc[nt][e_], act));
+    }
+}
+
 template <typename T>
 __global__ void moe_combine_kernel(T* __restrict__ out, const float* __restrict__ y, const int* __restrict__ place,
                                    const float* __restrict__ pair_w, int top, int N) {
@@ -254,6 +370,25 @@ TS_API int ts_grouped_linear(void* out, const void* x, const void* w, const int*
   cudaStream_t s = (cudaStream_t)stream;
   dim3 grid(ceil_div(N, GL_BN), ceil_div(P, GL_BM) + E);
   if (grid.y > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_grouped_linear: %d rows too many for one launch", P);
+  if (dtype == TS_BF16 && K % 8 == 0 && !(((uintptr_t)x | (uintptr_t)w) & 15)) {
+    const size_t smem = (size_t)GM_STAGES * (GM_BM + GM_BN) * GM_BK * 2;
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e1 = cudaFuncSetAttribute(grouped_linear_mma_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      cudaError_t e2 = cudaFuncSetAttribute(grouped_linear_mma_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e1 != cudaSuccess || e2 != cudaSuccess) TS_REFUSE((int)(e1 != cudaSuccess ? e1 : e2), "ts_grouped_linear: shared memory %zu", smem);
+      configured = true;
+    }
+    if (out_dtype == TS_BF16)
+      ts_launch(grouped_linear_mma_kernel<bf16>, dim3(grid), dim3(GM_WARPS * 32), smem, s, (bf16*)out, (const bf16*)x,
+                (const bf16*)w, order, row_scale, offsets, tiles, top, N, K, act);
+    else if (out_dtype == TS_F32)
+      ts_launch(grouped_linear_mma_kernel<float>, dim3(grid), dim3(GM_WARPS * 32), smem, s, (float*)out, (const bf16*)x,
+                (const bf16*)w, order, row_scale, offsets, tiles, top, N, K, act);
+    else
+      TS_REFUSE(TS_ERR_DTYPE, "ts_grouped_linear: dtype %d -> %d", dtype, out_dtype);
+    TS_LAUNCH_CHECK();
+  }
 #define TS_GLK(TI, TO)                                                                                           \
   ts_launch(grouped_linear_kernel<TI, TO>, dim3(grid), dim3(256), 0, s, (TO*)out, (const TI*)x, (const TI*)w, order, \
             row_scale, offsets, tiles, top, N, K, act)
@@ -265,7 +400,6 @@ TS_API int ts_grouped_linear(void* out, const void* x, const void* w, const int*
   TS_LAUNCH_CHECK();
 }
 
-// pair_w: [T * top] weights of the choices, or null (the weights went into the experts' inputs).
 TS_API int ts_moe_combine(void* out, const float* y, const int* place, const float* pair_w, int T, int top, int N, int dtype,
                           void* stream) {
   if (T <= 0) return 0;

@@ -114,6 +114,7 @@ class CudaOps:
             "ts_lightning": [P, P, I, P, P, P, P, I, I, I, I, I, P],
             "ts_kv_write_pair": [P, I, I, I, P, P, P, I, I, I, I, I, I, P],
             "ts_attention_diff": [P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, F, F, I, P],
+            "ts_attention_diff_mma": [P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, F, F, P],
             "ts_router_topk": [P, P, P, P, I, I, I, I, I, I, I, P],
             "ts_moe_align": [P, I, I, P, P, P, P, P],
             "ts_grouped_linear": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
@@ -123,6 +124,8 @@ class CudaOps:
             fn = getattr(self.lib, name)
             fn.argtypes = args
             fn.restype = c_int
+        self.lib.ts_attention_diff_mma_supported.argtypes = [I, I, I, I, I]
+        self.lib.ts_attention_diff_mma_supported.restype = c_int
         self.lib.ts_moe_tile_rows.argtypes = []
         self.lib.ts_moe_tile_rows.restype = c_int
         self.lib.ts_attention_decode_supported.argtypes = [I, I, I, I]
@@ -581,7 +584,17 @@ class CudaOps:
                        page_size: int, scale: float, lam: float, eps: float, out_scale: float) -> None:
         """out [T, H V] = out_scale * rmsnorm_head(a1 - lam a2): two causal softmax maps a head (queries in
         the first H 2D columns of ``proj`` as [map 1 | map 2] per head, cached key rows 2D wide) over the
-        same cached values."""
+        same cached values.  bfloat16 with maps of 32 or 64 and values of 64 or 128: the tensor-core kernel;
+        anything else: the any-size kernel."""
+        if (self.use_fast_attention and proj.dtype == torch.bfloat16
+                and self.lib.ts_attention_diff_mma_supported(H, KVH, D, V, _code(proj.dtype))):
+            rc = self.lib.ts_attention_diff_mma(
+                _ptr(out), _ptr(proj), proj.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+                _ptr(step.q_start), _ptr(step.seq_lens), step.num_requests, block_tables.shape[1], step.max_q_len, H,
+                KVH, D, V, page_size, float(scale), float(lam), float(eps), float(out_scale), self._stream())
+            if rc != self.UNSUPPORTED:
+                self._check(rc, "attention_diff_mma")
+                return
         self._check(self.lib.ts_attention_diff(
             _ptr(out), _ptr(proj), proj.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(step.q_start),
             _ptr(step.seq_lens), step.num_requests, block_tables.shape[1], step.max_q_len, H, KVH, D, V, page_size,
