@@ -145,7 +145,7 @@ def make_model(shape: str, layers: int, tmp: str) -> str:
 
 
 def build_engine_on_device(shape: str, layers: int, *, ctx_len: int, page: int, max_seqs: int, max_tokens: int,
-                           graph_sizes: tuple[int, ...], model=None, portion_budget: int | None = None):
+                           graph_sizes: tuple[int, ...], model=None, portion_budget: int | None = None, mcfg=None):
     """An engine around a model whose N(0, 0.02) weights are drawn on the device (no checkpoint file:
     the 14B shape would be 30 GB of it); everything else as ``LLMEngine.from_config`` builds it."""
     import torch
@@ -158,9 +158,10 @@ def build_engine_on_device(shape: str, layers: int, *, ctx_len: int, page: int, 
     from turingserve_b200.sampling.sampler import Sampler
     from turingserve_b200.weights.random_init import random_model_on_device
 
-    kw = dict(SHAPES[shape])
-    kw["num_layers"] = layers
-    mcfg = make_config(**kw)
+    if mcfg is None:
+        kw = dict(SHAPES[shape])
+        kw["num_layers"] = layers
+        mcfg = make_config(**kw)
     device = torch.device("cuda", 0)
     if model is None:
         t0 = time.time()
@@ -595,6 +596,213 @@ class _StubTokenizer:
         return ""
 
 
+# ---- another design beside the flagship: Komirax (linear attention with a decaying state, two-map attention,
+# dense and routed feed-forwards) at layer sizes of real models, next to Qwen2 layers of the same width --------
+KOMIRAX_SIZES = {
+    # width, heads, kv heads, key width per map / per linear head, value width, dense ff, experts, top, expert ff,
+    # and the Qwen2 shape whose layers stand beside it
+    "1.5b": dict(width=1536, heads=12, kv_heads=2, dim=64, vdim=128, ldim=128, ff=13440, experts=8, top=2, eff=2688,
+                 beside="qwen2.5-1.5b"),
+    "7b": dict(width=3584, heads=28, kv_heads=4, dim=64, vdim=128, ldim=128, ff=28416, experts=8, top=2, eff=7104,
+               beside="qwen2.5-7b"),
+}
+
+
+def komirax_config(z: dict, groups: int, vocab: int):
+    """``groups`` times four layers: (linear, dense), (linear, routed), (two-map attention, routed), (two-map
+    attention, dense)."""
+    from turingserve_b200.models.komirax import make_config
+    lin = {"type": "lightning", "mixer": {"heads": z["heads"], "dim": z["ldim"], "vdim": z["vdim"],
+                                          "decay": [1.0 - 2.0 ** -(2 + 6 * i / max(1, z["heads"] - 1)) for i in range(z["heads"])]}}
+    att = {"type": "attention", "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"],
+                                          "diff": 0.5, "scale": z["dim"] ** -0.5}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["eff"]}, "router": {"experts": z["experts"], "top": z["top"]}}
+    four = [{**lin, "mlp": dense}, {**lin, "mlp": moe}, {**att, "mlp": moe}, {**att, "mlp": dense}]
+    return make_config(width=z["width"], vocab=vocab, layers=four * groups, eps=1e-6)
+
+
+def timed(fn, flush, reps: int = 7) -> float:
+    """Median device time of ``fn`` in ms: captured once into a CUDA graph (so that the host's launch cost of a
+    few-microsecond kernel is not what is timed) and replayed with the L2 flushed before every repetition
+    (``flush`` writes a buffer larger than L2)."""
+    import torch
+    fn()                                                     # work buffers are made outside the capture
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    out = []
+    for i in range(reps + 3):
+        flush()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            out.append(e0.elapsed_time(e1))
+    return sorted(out)[len(out) // 2]
+
+
+def komirax_kernels(ops, z: dict, pk: dict, T: int, B: int, ctx: int, page: int) -> dict:
+    """Each kernel of the new mechanisms alone: a portion of T tokens and B single tokens at context ``ctx``."""
+    import torch
+    from types import SimpleNamespace
+    dev = torch.device("cuda", 0)
+    big = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    flush = lambda: big.fill_(1)
+    H, G, D, V, LD, W = z["heads"], z["kv_heads"], z["dim"], z["vdim"], z["ldim"], z["width"]
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    out = {}
+    FP32_PEAK = 148 * 128 * 2 * 1.965e9                      # FFMA lanes x 2 x the highest SM clock: nominal
+    hbm = pk["hbm_gbs"] * 1e9
+
+    # the state scan
+    for name, rows, reqs in (("prefill", T, 1), ("decode", B, B)):
+        proj = torch.randn(rows, 2 * H * LD + 2 * H * V, device=dev).to(torch.bfloat16)
+        state = torch.zeros(reqs + 1, H, LD, V, device=dev)
+        decay = torch.full((H,), 0.99, device=dev)
+        o = torch.empty(rows, H * V, device=dev)
+        per = rows // reqs
+        step = SimpleNamespace(q_start=i32([i * per for i in range(reqs + 1)]), state_slots=i32(list(range(reqs))), num_requests=reqs)
+        ms = timed(lambda: ops.lightning(o, proj, state, decay, step, H, LD, V), flush)
+        flops = 5.0 * rows * H * LD * V
+        byts = 2.0 * reqs * H * LD * V * 4 + rows * (2 * H * LD + H * V) * 2 + rows * H * V * 4
+        out[f"state_scan_{name}"] = {"us": round(ms * 1e3, 1), "tflops_fp32": round(flops / ms / 1e9, 2),
+                                     "frac_of_fp32_ffma_nominal": round(flops / (ms / 1e3) / FP32_PEAK, 3),
+                                     "frac_of_hbm": round(byts / (ms / 1e3) / hbm, 3)}
+
+    # the two-map attention
+    pages = B * (-(-(ctx + 1) // page)) + -(-T // page) + 2
+    kc = torch.randn(pages, G, page, 2 * D, device=dev).to(torch.bfloat16)
+    vc = torch.randn(pages, G, page, V, device=dev).to(torch.bfloat16)
+    width = -(-max(ctx + 1, T) // page)
+    for name, reqs, per, seq in (("prefill", 1, T, T), ("decode", B, 1, ctx + 1)):
+        rows = reqs * per
+        proj = torch.randn(rows, H * 2 * D + G * 2 * D + G * V, device=dev).to(torch.bfloat16)
+        tables = torch.zeros(reqs, width, dtype=torch.int32, device=dev)
+        n = -(-seq // page)
+        for r in range(reqs):
+            tables[r, :n] = torch.arange(1 + r * n, 1 + (r + 1) * n, dtype=torch.int32, device=dev)
+        step = SimpleNamespace(q_start=i32([i * per for i in range(reqs + 1)]), seq_lens=i32([seq] * reqs), num_requests=reqs,
+                               max_q_len=per)
+        o = torch.empty(rows, H * V, dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: ops.attention_diff(o, proj, kc, vc, tables, step, H, G, D, V, page, D ** -0.5, 0.4, 1e-6, 0.5), flush)
+        flops = 2.0 * (2 * D + 2 * V) * H * (per * (per + 1) / 2 + per * (seq - per)) * reqs
+        byts = reqs * seq * G * (2 * D + V) * 2.0
+        out[f"two_map_attention_{name}"] = {"us": round(ms * 1e3, 1), "tflops": round(flops / ms / 1e9, 1),
+                                            "frac_of_bf16": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 3),
+                                            "frac_of_hbm": round(byts / (ms / 1e3) / hbm, 3)}
+
+    # the routed feed-forward: router + sort, the two grouped products
+    E, top, ff = z["experts"], z["top"], z["eff"]
+    w_up = (torch.randn(E, ff, W, device=dev) * 0.02).to(torch.bfloat16)
+    w_down = (torch.randn(E, W, ff, device=dev) * 0.02).to(torch.bfloat16)
+    wr = torch.randn(E, W, device=dev) * 0.05
+    for name, rows in (("prefill", T), ("decode", B)):
+        x = torch.randn(rows, W, device=dev).to(torch.bfloat16)
+        idx = torch.empty(rows, top, dtype=torch.int32, device=dev)
+        wts = torch.empty(rows, top, device=dev)
+        a_ = torch.empty(rows * top, ff, dtype=torch.bfloat16, device=dev)
+        y = torch.empty(rows * top, W, device=dev)
+        ops.router_topk(idx, wts, x, wr, False, False)
+        offsets, order, place, tiles = ops.moe_align(idx, E)
+        ms_r = timed(lambda: (ops.router_topk(idx, wts, x, wr, False, False), ops.moe_align(idx, E)), flush)
+        ms_u = timed(lambda: ops.grouped_linear(a_, x, w_up, order, wts, offsets, tiles, top, "relu2"), flush)
+        ms_d = timed(lambda: ops.grouped_linear(y, a_, w_down, None, None, offsets, tiles, 1), flush)
+        flops = 2.0 * rows * top * ff * W
+        used = min(E, rows * top)
+        byts = used * ff * W * 2.0
+        out[f"routed_ff_{name}"] = {
+            "router_and_sort_us": round(ms_r * 1e3, 1), "up_us": round(ms_u * 1e3, 1), "down_us": round(ms_d * 1e3, 1),
+            "up_tflops": round(flops / ms_u / 1e9, 1), "down_tflops": round(flops / ms_d / 1e9, 1),
+            "up_frac_of_bf16": round(flops / (ms_u / 1e3) / (pk["bf16_tflops"] * 1e12), 3),
+            "up_frac_of_hbm": round(byts / (ms_u / 1e3) / hbm, 3), "down_frac_of_hbm": round(byts / (ms_d / 1e3) / hbm, 3)}
+    return out
+
+
+def run_design(a) -> dict:
+    """``--design komirax``: prefill and decode throughput of Komirax layers beside Qwen2 layers of the same
+    width and count (random weights, bfloat16, through the step function), and each new kernel alone."""
+    import numpy as np
+    import torch
+
+    from turingserve_b200 import kernels
+    from turingserve_b200.engine.batch import StepEntry
+
+    torch.cuda.set_device(0)
+    ops = kernels.ops()
+    pk, pk_src = peaks()
+    rng = np.random.default_rng(0)
+    B, T, ctx, page = a.batch, a.prefill_tokens, a.prompt_len, 64
+    steps, warmup = min(a.steps, 64), max(3, a.warmup)
+    vocab = 32768
+    result = {"design": "komirax", "dtype": "bfloat16", "data": "synthetic", "peaks": pk_src, "batch": B,
+              "prefill_tokens": T, "context": ctx, "page": page, "sizes": {}}
+
+    def measure(eng):
+        runner, cache = eng.runner, eng.cache
+        toks = rng.integers(0, vocab, size=T).tolist()
+        times = []
+        for i in range(6):
+            rc = cache.admit("p")
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            runner.step([StepEntry(rc, toks, [T - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            cache.release(rc)
+            if i >= 3:
+                times.append(e0.elapsed_time(e1))
+        pms = sorted(times)[1]
+        rcs = [cache.admit(f"d{i}") for i in range(B)]
+        for rc in rcs:
+            runner.step([StepEntry(rc, rng.integers(0, vocab, size=ctx).tolist(), [])])
+        dt = rng.integers(0, vocab, size=(warmup + steps, B))
+        for s_ in range(warmup):
+            runner.step([StepEntry(rc, [int(dt[s_, i])], [0]) for i, rc in enumerate(rcs)])
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for s_ in range(warmup, warmup + steps):
+            runner.step([StepEntry(rc, [int(dt[s_, i])], [0]) for i, rc in enumerate(rcs)])
+        e1.record()
+        torch.cuda.synchronize()
+        dms = e0.elapsed_time(e1) / steps
+        for rc in rcs:
+            cache.release(rc)
+        return {"prefill_ms": round(pms, 3), "prefill_tok_s": round(T / (pms / 1e3), 1), "decode_ms_per_step": round(dms, 4),
+                "decode_tok_s": round(B / (dms / 1e3), 1)}
+
+    for name in a.design_sizes.split(","):
+        z = KOMIRAX_SIZES[name]
+        groups = a.layers // 4 if a.layers else 2
+        ctx_len = max(ctx + warmup + steps + 64, T + 64)
+        kcfg = komirax_config(z, groups, vocab)
+        eng = build_engine_on_device(f"komirax-{name}", 4 * groups, ctx_len=ctx_len, page=page, max_seqs=B,
+                                     max_tokens=max(T, ctx), graph_sizes=(B,), mcfg=kcfg)
+        ours = measure(eng)
+        del eng
+        torch.cuda.empty_cache()
+        qkw = dict(SHAPES[z["beside"]])
+        qkw.update(num_layers=4 * groups, vocab_size=vocab, tie_word_embeddings=False)
+        from turingserve_b200.models.qwen2 import make_config as qwen_config
+        eng = build_engine_on_device(z["beside"], 4 * groups, ctx_len=ctx_len, page=page, max_seqs=B,
+                                     max_tokens=max(T, ctx), graph_sizes=(B,), mcfg=qwen_config(**qkw))
+        beside = measure(eng)
+        del eng
+        torch.cuda.empty_cache()
+        entry = {"layers": 4 * groups, "width": z["width"], "komirax": ours, "beside": z["beside"], "qwen2": beside,
+                 "prefill_ratio": round(ours["prefill_tok_s"] / beside["prefill_tok_s"], 3),
+                 "decode_ratio": round(ours["decode_tok_s"] / beside["decode_tok_s"], 3)}
+        if "kernels" in a.phases.split(","):
+            entry["kernels"] = komirax_kernels(ops, z, pk, T, B, ctx, page)
+        result["sizes"][name] = entry
+    result["gpu_launches"] = ops.launches
+    return result
+
+
 def run_reference(a) -> dict:
     """The unmodified reference from baseline/_ref through its own ``build_engine`` /
     ``LLMEngine.step``: float16 (it has no bfloat16), Triton kernels, CUDA graphs, same workload."""
@@ -677,10 +885,17 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--phases", default="prefill,decode,points,e2e,kernels,mixed",
                     help="which measurements to run (decode always runs); fewer for a profiler capture")
+    ap.add_argument("--design", default="", choices=["", "komirax"],
+                    help="instead of the default workload: layers of this design beside Qwen2 layers of the same width "
+                         "(prefill and decode throughput, and each of the design's kernels alone)")
+    ap.add_argument("--design-sizes", default="1.5b,7b", help="which of the design's layer sizes to run")
     a = ap.parse_args()
     if a.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
         return 2
+    if a.design:
+        print(json.dumps(run_design(a)))
+        return 0
     out = run_reference(a) if a.impl == "reference" else run_ours(a)
     print(json.dumps(out))
     return 0

@@ -10,9 +10,13 @@
 // online softmax (32-bit, exponentials in base 2), O_m += P V with P rounded to bfloat16 as an operand.
 // At the end o = O_1 / l_1 - lambda O_2 / l_2, divided by its root mean square over V, times out_scale.
 //
-// A block whose rows all fit one warp (a request's single token, G <= 16) lets its four warps take every
-// fourth key tile each for the SAME rows and merges the four partial results through shared memory, so a
-// decoding request's keys are read by four warps instead of one.
+// A block whose rows all fit one warp (a request's single token, G <= 16) lets its four warps work for the
+// SAME rows: warp w takes keys 16 w .. 16 w + 15 of every tile, and the four partial results (each with its own
+// running maximum and sum) are merged through shared memory at the end, so a decoding request's keys are
+// shared by four warps instead of waiting for one.  Such a request's keys are also cut over up to `max_splits`
+// blocks (the grid's x index, which for a portion counts its row tiles): every block leaves its partial result
+// in scratch, and the block that comes last for a (request, kv head) (a ticket counter; nobody waits) folds the
+// partial results in split order and writes the output.
 #include "common.cuh"
 #include "mma_utils.cuh"
 
@@ -22,6 +26,7 @@ constexpr int DM_WARPS = 4;
 constexpr int DM_ROWS = DM_WARPS * 16;
 constexpr int DM_TILE = 64;
 constexpr int DM_STAGES = 3;
+constexpr int DM_PAGES_S = 2048;          // block-table entries a block keeps in shared memory
 constexpr float DM_LOG2E = 1.4426950408889634f;
 
 template <int D, int V>
@@ -30,7 +35,8 @@ attention_diff_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ proj,
                           const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                           const int* __restrict__ block_tables, const int* __restrict__ q_start,
                           const int* __restrict__ seq_lens, int table_width, int H, int KVH, int page, float scale,
-                          float lambda, float eps, float out_scale) {
+                          float lambda, float eps, float out_scale, float* __restrict__ scratch,
+                          int* __restrict__ counters, int max_splits) {
   pdl_launch_dependents();
   pdl_wait();
   constexpr int DK = 2 * D;                 // a cached key row
@@ -44,11 +50,17 @@ attention_diff_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ proj,
   const int seq_len = seq_lens[b];
   const int n_rows = q_len * G;
   const int n_row_tiles = (n_rows + DM_ROWS - 1) / DM_ROWS;
-  if ((int)blockIdx.x >= n_row_tiles) return;
-  const int row0 = (n_row_tiles - 1 - blockIdx.x) * DM_ROWS;        // longest tiles first
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int prefix = seq_len - q_len;
   const bool split = n_rows <= 16;                                   // every warp works for rows 0..15
+  const int prefix = seq_len - q_len;
+  // a split request: the grid's x index is the piece of its keys; a portion: its row tile
+  int nsplit = 1;
+  if (split && n_rows > 0 && scratch != nullptr) {
+    const int all_tiles = seq_len > 0 ? (prefix + (n_rows - 1) / G) / DM_TILE + 1 : 0;
+    nsplit = max(1, min(min((int)gridDim.x, max_splits), all_tiles));
+  }
+  if ((int)blockIdx.x >= (split ? nsplit : n_row_tiles)) return;
+  const int row0 = split ? 0 : (n_row_tiles - 1 - blockIdx.x) * DM_ROWS;      // longest tiles first
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int rw = split ? 0 : warp;
 
   unsigned char* k_s = smem;
@@ -92,25 +104,35 @@ attention_diff_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ proj,
   const int w_first = row0 + rw * 16, w_last = min(w_first + 15, n_rows - 1);
   const int w_pos_lo = prefix + w_first / G, w_pos_hi = (w_first < n_rows) ? prefix + w_last / G : -1;
 
+  // the request's block table, once, in shared memory: no dependent global load per key
+  __shared__ int pages_s[DM_PAGES_S];
+  const int n_pages = n_tiles > 0 ? j_hi / page + 1 : 0;
+  const bool pages_staged = n_pages <= DM_PAGES_S;
+  if (pages_staged) {
+    for (int i = threadIdx.x; i < n_pages; i += DM_WARPS * 32) pages_s[i] = block_tables[(size_t)b * table_width + i];
+    __syncthreads();
+  }
+  const int page_shift = (page & (page - 1)) == 0 ? 31 - __clz(page) : -1;
+
+  // two threads a key: each brings every other 16-byte piece of the key row and of the value row
   auto load_tile = [&](int tile, int stage) {
-    const int j0 = tile * DM_TILE;
+    const int key = threadIdx.x >> 1, half = threadIdx.x & 1;
+    const int j = tile * DM_TILE + key;
+    const bool ok = j <= j_hi;
+    size_t slot = 0;
+    if (ok) {
+      const int lp = page_shift >= 0 ? (j >> page_shift) : (j / page);
+      const int pg = pages_staged ? pages_s[lp] : block_tables[(size_t)b * table_width + lp];
+      slot = ((size_t)pg * KVH + kvh) * page + (size_t)(j - lp * page);
+    }
     unsigned char* ks_ = k_s + stage * K_STAGE;
     unsigned char* vs_ = v_s + stage * V_STAGE;
-    for (int idx = threadIdx.x; idx < DM_TILE * (CHK + CHV); idx += DM_WARPS * 32) {
-      const int key = idx / (CHK + CHV), c = idx % (CHK + CHV);
-      const int j = j0 + key;
-      const bool ok = j <= j_hi;
-      size_t slot = 0;
-      if (ok) {
-        const int lp = j / page;
-        const int pg = block_tables[(size_t)b * table_width + lp];
-        slot = ((size_t)pg * KVH + kvh) * page + (size_t)(j - lp * page);
-      }
-      if (c < CHK)
-        cp_async_16(ks_ + swz<DK>(key, c), k_cache + slot * DK + c * 8, ok);
-      else
-        cp_async_16(vs_ + swz<V>(key, c - CHK), v_cache + slot * V + (c - CHK) * 8, ok);
-    }
+    const bf16* ksrc = k_cache + slot * DK;
+    const bf16* vsrc = v_cache + slot * V;
+#pragma unroll
+    for (int c = 0; c < CHK / 2; ++c) cp_async_16(ks_ + swz<DK>(key, 2 * c + half), ksrc + (2 * c + half) * 8, ok);
+#pragma unroll
+    for (int c = 0; c < CHV / 2; ++c) cp_async_16(vs_ + swz<V>(key, 2 * c + half), vsrc + (2 * c + half) * 8, ok);
   };
 
   float o[2][NT][4];
@@ -124,21 +146,24 @@ attention_diff_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ proj,
   }
   const float sc = scale * DM_LOG2E;
 
+  const int per_split = (n_tiles + nsplit - 1) / nsplit;
+  const int t_begin = nsplit > 1 ? (int)blockIdx.x * per_split : 0;
+  const int t_end = nsplit > 1 ? min(n_tiles, t_begin + per_split) : n_tiles;
 #pragma unroll
   for (int s = 0; s < DM_STAGES - 1; ++s) {
-    if (s < n_tiles) load_tile(s, s);
+    if (t_begin + s < t_end) load_tile(t_begin + s, s);
     cp_async_commit();
   }
-  for (int t = 0; t < n_tiles; ++t) {
-    if (t + DM_STAGES - 1 < n_tiles) load_tile(t + DM_STAGES - 1, (t + DM_STAGES - 1) % DM_STAGES);
+  for (int t = t_begin; t < t_end; ++t) {
+    const int at = t - t_begin;
+    if (t + DM_STAGES - 1 < t_end) load_tile(t + DM_STAGES - 1, (at + DM_STAGES - 1) % DM_STAGES);
     cp_async_commit();
     cp_async_wait<DM_STAGES - 1>();
     __syncthreads();
-    const unsigned char* ks_ = k_s + (t % DM_STAGES) * K_STAGE;
-    const unsigned char* vs_ = v_s + (t % DM_STAGES) * V_STAGE;
+    const unsigned char* ks_ = k_s + (at % DM_STAGES) * K_STAGE;
+    const unsigned char* vs_ = v_s + (at % DM_STAGES) * V_STAGE;
     const int j0 = t * DM_TILE;
-    const bool mine = !split || (t % DM_WARPS) == warp;
-    if (mine && j0 <= w_pos_hi) {                                    // else the tile lies in these rows' future (warp-uniform)
+    if (j0 <= w_pos_hi) {                                    // else the tile lies in these rows' future (warp-uniform)
       const bool need_mask = (j0 + DM_TILE - 1 > w_pos_lo) || (j0 + DM_TILE - 1 > j_hi);
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
@@ -149,6 +174,7 @@ attention_diff_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ proj,
         for (int ks = 0; ks < KS; ++ks) {
 #pragma unroll
           for (int np = 0; np < DM_TILE / 16; ++np) {
+            if (split && np != warp) continue;                       // (warp-uniform) this warp's 16 keys only
             const int mat = lane >> 3, r = lane & 7;
             const int key = np * 16 + (mat >> 1) * 8 + r;
             const int ch = c * (D / 8) + ks * 2 + (mat & 1);
@@ -160,7 +186,8 @@ attention_diff_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ proj,
         }
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int nt = 0; nt < DM_TILE / 8; ++nt)
+        for (int nt = 0; nt < DM_TILE / 8; ++nt) {
+          if (split && (nt >> 1) != warp) continue;                // another warp's keys: not computed, not used
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             float v = s_acc[nt][e] * sc;
@@ -171,6 +198,7 @@ attention_diff_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ proj,
             s_acc[nt][e] = v;
             mx[e >> 1] = fmaxf(mx[e >> 1], v);
           }
+        }
         float corr[2], m_use[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
@@ -183,13 +211,15 @@ attention_diff_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ proj,
         }
         float rs[2] = {0.f, 0.f};
 #pragma unroll
-        for (int nt = 0; nt < DM_TILE / 8; ++nt)
+        for (int nt = 0; nt < DM_TILE / 8; ++nt) {
+          if (split && (nt >> 1) != warp) continue;
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const float p = exp2f(s_acc[nt][e] - m_use[e >> 1]);
             s_acc[nt][e] = p;
             rs[e >> 1] += p;
           }
+        }
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
           rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 1);
@@ -205,6 +235,7 @@ attention_diff_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ proj,
         }
 #pragma unroll
         for (int kk = 0; kk < DM_TILE / 16; ++kk) {
+          if (split && kk != warp) continue;
           unsigned pf[4];
           pf[0] = pack_bf16(s_acc[2 * kk][0], s_acc[2 * kk][1]);
           pf[1] = pack_bf16(s_acc[2 * kk][2], s_acc[2 * kk][3]);
@@ -233,42 +264,99 @@ attention_diff_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ proj,
     float* xs = reinterpret_cast<float*>(smem);
     __syncthreads();
     if (warp > 0) {
-      float* mine_ = xs + ((size_t)(warp - 1) * 32 + lane) * PER;
+      float* mine_ = xs + (size_t)(warp - 1) * 32 * PER + lane;
 #pragma unroll
       for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-          mine_[c * 2 + r] = m_run[c][r];
-          mine_[4 + c * 2 + r] = l_run[c][r];
+          mine_[(c * 2 + r) * 32] = m_run[c][r];
+          mine_[(4 + c * 2 + r) * 32] = l_run[c][r];
         }
 #pragma unroll
       for (int c = 0; c < 2; ++c)
 #pragma unroll
         for (int i = 0; i < NT; ++i)
 #pragma unroll
-          for (int e = 0; e < 4; ++e) mine_[8 + (c * NT + i) * 4 + e] = o[c][i][e];
+          for (int e = 0; e < 4; ++e) mine_[(8 + (c * NT + i) * 4 + e) * 32] = o[c][i][e];
     }
     __syncthreads();
     if (warp > 0) return;
     for (int w = 0; w < DM_WARPS - 1; ++w) {
-      const float* theirs = xs + ((size_t)w * 32 + lane) * PER;
+      const float* theirs = xs + (size_t)w * 32 * PER + lane;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         float fa[2], fb[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
-          const float ma = m_run[c][r], mb = theirs[c * 2 + r];
+          const float ma = m_run[c][r], mb = theirs[(c * 2 + r) * 32];
           const float m_new = fmaxf(ma, mb);
           fa[r] = (ma == -INFINITY) ? 0.f : exp2f(ma - m_new);
           fb[r] = (mb == -INFINITY) ? 0.f : exp2f(mb - m_new);
-          l_run[c][r] = l_run[c][r] * fa[r] + theirs[4 + c * 2 + r] * fb[r];
+          l_run[c][r] = l_run[c][r] * fa[r] + theirs[(4 + c * 2 + r) * 32] * fb[r];
           m_run[c][r] = m_new;
         }
 #pragma unroll
         for (int i = 0; i < NT; ++i)
 #pragma unroll
           for (int e = 0; e < 4; ++e)
-            o[c][i][e] = o[c][i][e] * fa[e >> 1] + theirs[8 + (c * NT + i) * 4 + e] * fb[e >> 1];
+            o[c][i][e] = o[c][i][e] * fa[e >> 1] + theirs[(8 + (c * NT + i) * 4 + e) * 32] * fb[e >> 1];
+      }
+    }
+  }
+
+  if (nsplit > 1) {
+    // (only warp 0 is left) this block's partial result to scratch; the last block of the (request, kv head) folds
+    // all of them in split order
+    constexpr int PER = 8 + 8 * NT;
+    const size_t group = (size_t)b * KVH + kvh;
+    float* mine_ = scratch + (group * max_splits + blockIdx.x) * 32 * PER + lane;
+#pragma unroll
+    for (int c = 0; c < 2; ++c)
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        mine_[(c * 2 + r) * 32] = m_run[c][r];
+        mine_[(4 + c * 2 + r) * 32] = l_run[c][r];
+      }
+#pragma unroll
+    for (int c = 0; c < 2; ++c)
+#pragma unroll
+      for (int i = 0; i < NT; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) mine_[(8 + (c * NT + i) * 4 + e) * 32] = o[c][i][e];
+    __threadfence();
+    __syncwarp();
+    int ticket = 0;
+    if (lane == 0) ticket = atomicAdd(&counters[group], 1);
+    ticket = __shfl_sync(0xffffffffu, ticket, 0);
+    if (ticket != nsplit - 1) return;
+    __threadfence();
+    if (lane == 0) counters[group] = 0;                      // ready for the next launch
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+#pragma unroll
+      for (int i = 0; i < NT; ++i) o[c][i][0] = o[c][i][1] = o[c][i][2] = o[c][i][3] = 0.f;
+      m_run[c][0] = m_run[c][1] = -INFINITY;
+      l_run[c][0] = l_run[c][1] = 0.f;
+    }
+    for (int w = 0; w < nsplit; ++w) {
+      const float* theirs = scratch + (group * max_splits + w) * 32 * PER + lane;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        float fa[2], fb[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const float ma = m_run[c][r], mb = __ldcg(theirs + (c * 2 + r) * 32);
+          const float m_new = fmaxf(ma, mb);
+          fa[r] = (ma == -INFINITY) ? 0.f : exp2f(ma - m_new);
+          fb[r] = (mb == -INFINITY) ? 0.f : exp2f(mb - m_new);
+          l_run[c][r] = l_run[c][r] * fa[r] + __ldcg(theirs + (4 + c * 2 + r) * 32) * fb[r];
+          m_run[c][r] = m_new;
+        }
+#pragma unroll
+        for (int i = 0; i < NT; ++i)
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            o[c][i][e] = o[c][i][e] * fa[e >> 1] + __ldcg(theirs + (8 + (c * NT + i) * 4 + e) * 32) * fb[e >> 1];
       }
     }
   }
@@ -303,7 +391,7 @@ template <int D, int V>
 int launch_diff_mma(bf16* out, const bf16* proj, int proj_stride, const bf16* k_cache, const bf16* v_cache,
                     const int* block_tables, const int* q_start, const int* seq_lens, int B, int table_width,
                     int max_q_len, int H, int KVH, int page, float scale, float lambda, float eps, float out_scale,
-                    cudaStream_t s) {
+                    float* scratch, int* counters, int max_splits, cudaStream_t s) {
   const size_t tiles = (size_t)DM_STAGES * DM_TILE * (2 * D + V) * 2;
   const size_t merge = (size_t)(DM_WARPS - 1) * 32 * (8 + V) * sizeof(float);
   const size_t smem = tiles > merge ? tiles : merge;
@@ -314,9 +402,11 @@ int launch_diff_mma(bf16* out, const bf16* proj, int proj_stride, const bf16* k_
     configured = true;
   }
   const int G = H / KVH;
-  dim3 grid(ceil_div(max_q_len * G, DM_ROWS), KVH, B);
+  if (scratch == nullptr || counters == nullptr || G > 16) max_splits = 1;
+  dim3 grid(max(ceil_div(max_q_len * G, DM_ROWS), max_splits), KVH, B);
   ts_launch(attention_diff_mma_kernel<D, V>, dim3(grid), dim3(DM_WARPS * 32), smem, s, out, proj, proj_stride, k_cache,
-            v_cache, block_tables, q_start, seq_lens, table_width, H, KVH, page, scale, lambda, eps, out_scale);
+            v_cache, block_tables, q_start, seq_lens, table_width, H, KVH, page, scale, lambda, eps, out_scale,
+            max_splits > 1 ? scratch : nullptr, counters, max_splits);
   TS_LAUNCH_CHECK();
 }
 
@@ -326,11 +416,19 @@ TS_API int ts_attention_diff_mma_supported(int H, int KVH, int D, int V, int dty
   return dtype == TS_BF16 && KVH > 0 && H % KVH == 0 && (D == 32 || D == 64) && (V == 64 || V == 128);
 }
 
+// Floats of scratch the kernel wants for `max_splits` pieces of the keys of B requests' single tokens.
+TS_API long long ts_attention_diff_mma_scratch_floats(int B, int KVH, int V, int max_splits) {
+  return (long long)B * KVH * max_splits * 32 * (8 + V);
+}
+
 // Arguments as ts_attention_diff; bfloat16 only; the projection rows and both caches 16-byte aligned.
+// scratch / counters (B * KVH ints, zero before the first launch; the kernel leaves them zero) / max_splits: requests
+// that bring one token have their keys cut over up to max_splits blocks; null or 1: never.
 TS_API int ts_attention_diff_mma(void* out, const void* proj, int proj_stride, const void* k_cache, const void* v_cache,
                                  const int* block_tables, const int* q_start, const int* seq_lens, int B,
                                  int table_width, int max_q_len, int H, int KVH, int D, int V, int page, float scale,
-                                 float lambda, float eps, float out_scale, void* stream) {
+                                 float lambda, float eps, float out_scale, float* scratch, int* counters,
+                                 int max_splits, void* stream) {
   if (B <= 0 || max_q_len <= 0) return 0;
   if (!ts_attention_diff_mma_supported(H, KVH, D, V, TS_BF16))
     TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_attention_diff_mma: H=%d KVH=%d D=%d V=%d is not taken by this kernel", H, KVH, D, V);
@@ -342,7 +440,7 @@ TS_API int ts_attention_diff_mma(void* out, const void* proj, int proj_stride, c
   if (D == DD && V == VV)                                                                                            \
     return launch_diff_mma<DD, VV>((bf16*)out, (const bf16*)proj, proj_stride, (const bf16*)k_cache, (const bf16*)v_cache, \
                                    block_tables, q_start, seq_lens, B, table_width, max_q_len, H, KVH, page, scale,   \
-                                   lambda, eps, out_scale, s)
+                                   lambda, eps, out_scale, scratch, counters, max_splits, s)
   TS_DM(32, 64);
   TS_DM(32, 128);
   TS_DM(64, 64);

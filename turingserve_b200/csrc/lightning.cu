@@ -10,24 +10,26 @@
 // portions alike, so how a prompt is cut never changes a bit.  The columns of S are independent of one
 // another: one block owns LT_COLS columns of one (head, request) and keeps them in REGISTERS over all tokens
 // of the step: thread (part, col) holds rows part * LT_ROWS .. of column col.  Tokens arrive in groups of
-// LT_GROUP rows staged (and activated) in shared memory; a group's partial outputs of the row parts are
-// summed through shared memory, in part order.  Per token a thread does 3 * LT_ROWS 32-bit operations on
-// registers with two broadcast loads from shared memory.
+// LT_GROUP rows: the raw projection rows of the NEXT group are on their way (cp.async, 16 bytes a copy) while
+// the present group is computed; a group is activated out of the raw buffer into 32-bit shared memory; its
+// partial outputs of the row parts are summed through shared memory, in part order.  Per token a thread does
+// 3 * LT_ROWS 32-bit operations on registers with broadcast loads from shared memory.
 #include "common.cuh"
+#include "mma_utils.cuh"
 
 namespace {
 
 constexpr int LT_GROUP = 16;     // tokens staged at a time
-constexpr int LT_COLS = 32;      // state columns per block (one lane each)
-constexpr int LT_ROWS = 32;      // state rows per thread (registers)
+constexpr int LT_COLS = 16;      // state columns per block (half a warp: a warp holds two row parts)
+constexpr int LT_ROWS = 8;       // state rows per thread (registers)
 
-template <typename T> __device__ __forceinline__ float act_silu(float z) { return round_to<T>(z / (1.f + expf(-z))); }
+template <typename T> __device__ __forceinline__ float act_silu(float z) { return round_to<T>(silu_for<T>(z)); }
 
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(512)
 lightning_kernel(float* __restrict__ out, const T* __restrict__ proj, int proj_stride, float* __restrict__ state,
                  const float* __restrict__ decay, const int* __restrict__ q_start, const int* __restrict__ slots,
-                 int H, int D, int V, int parts) {
+                 int H, int D, int V, int parts, int fast_rows) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) float smem[];
@@ -52,19 +54,66 @@ lightning_kernel(float* __restrict__ out, const T* __restrict__ proj, int proj_s
     s[i] = (live && d < D) ? S[(size_t)d * V + j] : 0.f;
   }
   const int q_off = h * D, k_off = H * D + h * D, v_off = 2 * H * D + h * V;
-  for (int g0 = 0; g0 < n; g0 += LT_GROUP) {
+  // raw rows of a group, as stored: [2 buffers][LT_GROUP][D q | D k | LT_COLS v] (fast_rows: D a multiple of 8 and
+  // every piece 16-byte aligned, so the copies are asynchronous 16-byte ones; else plain loads at activation)
+  T* raw = reinterpret_cast<T*>(o_s + LT_GROUP * parts * LT_COLS);
+  const int raw_row = 2 * D + LT_COLS;
+  const int cols_here = min(LT_COLS, V - (int)blockIdx.x * LT_COLS);
+  constexpr int PER16 = 16 / (int)sizeof(T);
+  auto fetch = [&](int g0, int buf) {
+    if (!fast_rows) return;
     const int gn = min(LT_GROUP, n - g0);
-    __syncthreads();                                       // the group before has been summed and stored
+    const int chunks_qk = D / PER16, chunks_v = LT_COLS / PER16, per_row = 2 * chunks_qk + chunks_v;
+    for (int i = threadIdx.x; i < gn * per_row; i += blockDim.x) {
+      const int r = i / per_row, c = i % per_row;
+      const T* row = proj + (size_t)(t0 + g0 + r) * proj_stride;
+      T* dst = raw + ((size_t)buf * LT_GROUP + r) * raw_row;
+      if (c < chunks_qk) cp_async_16(dst + c * PER16, row + q_off + c * PER16, true);
+      else if (c < 2 * chunks_qk) cp_async_16(dst + D + (c - chunks_qk) * PER16, row + k_off + (c - chunks_qk) * PER16, true);
+      else {
+        const int cc = (c - 2 * chunks_qk) * PER16;
+        const bool ok = cc < cols_here;
+        cp_async_16(dst + 2 * D + cc, ok ? row + v_off + blockIdx.x * LT_COLS + cc : proj, ok);
+      }
+    }
+  };
+  fetch(0, 0);
+  cp_async_commit();
+  int buf = 0;
+  for (int g0 = 0; g0 < n; g0 += LT_GROUP, buf ^= 1) {
+    const int gn = min(LT_GROUP, n - g0);
+    if (g0 + LT_GROUP < n) fetch(g0 + LT_GROUP, buf ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();                                       // this group's raw rows are here; the group before is stored
     for (int i = threadIdx.x; i < gn * Dp; i += blockDim.x) {
       const int r = i / Dp, d = i % Dp;
-      const T* row = proj + (size_t)(t0 + g0 + r) * proj_stride;
-      q_s[i] = d < D ? act_silu<T>(to_f(row[q_off + d])) : 0.f;
-      k_s[i] = d < D ? act_silu<T>(to_f(row[k_off + d])) : 0.f;
+      float qv = 0.f, kv = 0.f;
+      if (d < D) {
+        if (fast_rows) {
+          const T* src = raw + ((size_t)buf * LT_GROUP + r) * raw_row;
+          qv = to_f(src[d]);
+          kv = to_f(src[D + d]);
+        } else {
+          const T* row = proj + (size_t)(t0 + g0 + r) * proj_stride;
+          qv = to_f(row[q_off + d]);
+          kv = to_f(row[k_off + d]);
+        }
+        qv = act_silu<T>(qv);
+        kv = act_silu<T>(kv);
+      }
+      q_s[i] = qv;
+      k_s[i] = kv;
     }
     for (int i = threadIdx.x; i < gn * LT_COLS; i += blockDim.x) {
       const int r = i / LT_COLS, c = i % LT_COLS;
-      const int jj = blockIdx.x * LT_COLS + c;
-      v_s[i] = jj < V ? act_silu<T>(to_f(proj[(size_t)(t0 + g0 + r) * proj_stride + v_off + jj])) : 0.f;
+      float vv = 0.f;
+      if (c < cols_here) {
+        vv = fast_rows ? to_f(raw[((size_t)buf * LT_GROUP + r) * raw_row + 2 * D + c])
+                       : to_f(proj[(size_t)(t0 + g0 + r) * proj_stride + v_off + blockIdx.x * LT_COLS + c]);
+        vv = act_silu<T>(vv);
+      }
+      v_s[i] = vv;
     }
     __syncthreads();
     for (int r = 0; r < gn; ++r) {
@@ -96,6 +145,7 @@ lightning_kernel(float* __restrict__ out, const T* __restrict__ proj, int proj_s
       out[(size_t)(t0 + g0 + r) * H * V + h * V + jj] = o;
     }
   }
+  cp_async_wait<0>();
 #pragma unroll
   for (int i = 0; i < LT_ROWS; ++i) {
     const int d = part * LT_ROWS + i;
@@ -112,10 +162,15 @@ TS_API int ts_lightning(float* out, const void* proj, int proj_stride, float* st
   if (B <= 0) return 0;
   if (H <= 0 || D <= 0 || V <= 0) TS_REFUSE(TS_ERR_SHAPE, "ts_lightning: %d heads of %d x %d", H, D, V);
   const int parts = ceil_div(D, LT_ROWS);
-  if (parts * LT_COLS > 256) TS_REFUSE(TS_ERR_LIMIT, "ts_lightning: keys of %d (limit %d)", D, 256 / LT_COLS * LT_ROWS);
+  if (parts * LT_COLS > 512) TS_REFUSE(TS_ERR_LIMIT, "ts_lightning: keys of %d (limit %d)", D, 512 / LT_COLS * LT_ROWS);
   if (B > 65535 || H > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_lightning: %d requests / %d heads per launch", B, H);
   cudaStream_t s = (cudaStream_t)stream;
-  const size_t smem = sizeof(float) * LT_GROUP * ((size_t)2 * parts * LT_ROWS + LT_COLS + (size_t)parts * LT_COLS);
+  const int elem = dtype == TS_F32 ? 4 : 2, per16 = 16 / elem;
+  // asynchronous 16-byte copies of the raw rows: every piece of a row (q, k, this block's v columns) must start on
+  // a 16-byte boundary in global and in shared memory
+  const int fast_rows = D % per16 == 0 && V % per16 == 0 && proj_stride % per16 == 0 && !((uintptr_t)proj & 15);
+  const size_t smem = sizeof(float) * LT_GROUP * ((size_t)2 * parts * LT_ROWS + LT_COLS + (size_t)parts * LT_COLS) +
+                      (size_t)2 * LT_GROUP * (2 * D + LT_COLS) * elem;
   dim3 grid(ceil_div(V, LT_COLS), H, B);
 #define TS_LT(TT)                                                                                                   \
   do {                                                                                                              \
@@ -126,7 +181,7 @@ TS_API int ts_lightning(float* out, const void* proj, int proj_stride, float* st
       configured = smem;                                                                                            \
     }                                                                                                               \
     ts_launch(lightning_kernel<TT>, dim3(grid), dim3(parts * LT_COLS), smem, s, out, (const TT*)proj, proj_stride, \
-              state, decay, q_start, slots, H, D, V, parts);                                                        \
+              state, decay, q_start, slots, H, D, V, parts, fast_rows);                                                        \
   } while (0)
   if (dtype == TS_F32) TS_LT(float);
   else if (dtype == TS_BF16) TS_LT(bf16);

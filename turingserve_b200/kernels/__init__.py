@@ -114,7 +114,7 @@ class CudaOps:
             "ts_lightning": [P, P, I, P, P, P, P, I, I, I, I, I, P],
             "ts_kv_write_pair": [P, I, I, I, P, P, P, I, I, I, I, I, I, P],
             "ts_attention_diff": [P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, F, F, I, P],
-            "ts_attention_diff_mma": [P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, F, F, P],
+            "ts_attention_diff_mma": [P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, F, F, P, P, I, P],
             "ts_router_topk": [P, P, P, P, I, I, I, I, I, I, I, P],
             "ts_moe_align": [P, I, I, P, P, P, P, P],
             "ts_grouped_linear": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
@@ -126,6 +126,8 @@ class CudaOps:
             fn.restype = c_int
         self.lib.ts_attention_diff_mma_supported.argtypes = [I, I, I, I, I]
         self.lib.ts_attention_diff_mma_supported.restype = c_int
+        self.lib.ts_attention_diff_mma_scratch_floats.argtypes = [I, I, I, I]
+        self.lib.ts_attention_diff_mma_scratch_floats.restype = ctypes.c_longlong
         self.lib.ts_moe_tile_rows.argtypes = []
         self.lib.ts_moe_tile_rows.restype = c_int
         self.lib.ts_attention_decode_supported.argtypes = [I, I, I, I]
@@ -555,6 +557,8 @@ class CudaOps:
         self._check(self.lib.ts_gated_rmsnorm(_ptr(out), _ptr(x), _ptr(gate), gate.stride(0), _ptr(weight), float(eps), T,
                                               n, _code(out.dtype), _code(weight.dtype), self._stream()), "gated_rmsnorm")
 
+    diff_decode_splits = int(os.environ.get("TURINGSERVE_B200_DIFF_DECODE_SPLITS", "16"))
+
     ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "relu2": 2, "silu": 3}
 
     def activation(self, out, x, kind: str) -> None:
@@ -588,10 +592,20 @@ class CudaOps:
         anything else: the any-size kernel."""
         if (self.use_fast_attention and proj.dtype == torch.bfloat16
                 and self.lib.ts_attention_diff_mma_supported(H, KVH, D, V, _code(proj.dtype))):
+            # requests that bring one token have their keys cut over so many blocks that every SM has two, sixteen
+            # at most (every piece is one more partial result for the last block to fold)
+            B = step.num_requests
+            splits = max(1, min(self.diff_decode_splits, 2 * self.num_sms // max(1, B * KVH)))
+            scratch = counters = None
+            if splits > 1:
+                scratch = self._buffer("diff_scratch", self.lib.ts_attention_diff_mma_scratch_floats(B, KVH, V, splits),
+                                       torch.float32, proj.device, floor=1 << 20)
+                counters = self._buffer("diff_counters", B * KVH, torch.int32, proj.device, floor=1 << 12, zero=True)
             rc = self.lib.ts_attention_diff_mma(
                 _ptr(out), _ptr(proj), proj.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
-                _ptr(step.q_start), _ptr(step.seq_lens), step.num_requests, block_tables.shape[1], step.max_q_len, H,
-                KVH, D, V, page_size, float(scale), float(lam), float(eps), float(out_scale), self._stream())
+                _ptr(step.q_start), _ptr(step.seq_lens), B, block_tables.shape[1], step.max_q_len, H,
+                KVH, D, V, page_size, float(scale), float(lam), float(eps), float(out_scale), _ptr(scratch),
+                _ptr(counters), splits, self._stream())
             if rc != self.UNSUPPORTED:
                 self._check(rc, "attention_diff_mma")
                 return
