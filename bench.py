@@ -709,13 +709,15 @@ def komirax_kernels(ops, z: dict, pk: dict, T: int, B: int, ctx: int, page: int)
         ops.router_topk(idx, wts, x, wr, False, False)
         offsets, order, place, tiles = ops.moe_align(idx, E)
         ms_r = timed(lambda: (ops.router_topk(idx, wts, x, wr, False, False), ops.moe_align(idx, E)), flush)
-        ms_u = timed(lambda: ops.grouped_linear(a_, x, w_up, order, wts, offsets, tiles, top, "relu2"), flush)
+        xs = torch.empty(rows * top, W, dtype=torch.bfloat16, device=dev)
+        ms_g = timed(lambda: ops.moe_gather(xs, x, order, wts, top), flush)
+        ms_u = timed(lambda: ops.grouped_linear(a_, xs, w_up, None, None, offsets, tiles, 1, "relu2"), flush)
         ms_d = timed(lambda: ops.grouped_linear(y, a_, w_down, None, None, offsets, tiles, 1), flush)
         flops = 2.0 * rows * top * ff * W
         used = min(E, rows * top)
         byts = used * ff * W * 2.0
         out[f"routed_ff_{name}"] = {
-            "router_and_sort_us": round(ms_r * 1e3, 1), "up_us": round(ms_u * 1e3, 1), "down_us": round(ms_d * 1e3, 1),
+            "router_and_sort_us": round(ms_r * 1e3, 1), "gather_us": round(ms_g * 1e3, 1), "up_us": round(ms_u * 1e3, 1), "down_us": round(ms_d * 1e3, 1),
             "up_tflops": round(flops / ms_u / 1e9, 1), "down_tflops": round(flops / ms_d / 1e9, 1),
             "up_frac_of_bf16": round(flops / (ms_u / 1e3) / (pk["bf16_tflops"] * 1e12), 3),
             "up_frac_of_hbm": round(byts / (ms_u / 1e3) / hbm, 3), "down_frac_of_hbm": round(byts / (ms_d / 1e3) / hbm, 3)}

@@ -351,3 +351,35 @@ def test_grouped_products_and_the_sum_of_choices(ops, dtype, T, E, top):
                 want[t] += o if on_input else wt * o
         t_ = dict(rtol=1e-4, atol=1e-4) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
         assert torch.allclose(out.float().cpu(), want, **t_), on_input
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_routed_part_many_row_path_equals_the_grouped_kernels(ops, dtype, monkeypatch):
+    """The routed feed-forward as a part: with every expert's rows launched as a product of their own (what steps
+    of many tokens do) and with the grouped kernels (what few tokens and captured steps do), against one token at a
+    time; three of six experts, one of them chosen by nobody."""
+    from turingserve_b200.config.model_config import RoutedMLPSpec
+    from turingserve_b200.parts.base import BuildContext
+    from turingserve_b200.parts.routed_mlp import RoutedMLP
+    g = torch.Generator(device=DEV).manual_seed(5)
+    W, ff, E, top, T = 64, 48, 6, 3, 90
+    part = RoutedMLP(RoutedMLPSpec(num_experts=E, top_k=top, intermediate_size=ff), BuildContext(W, dtype, torch.device(DEV), 0))
+    t = {"router": torch.randn(E, W, generator=g, device=DEV) * 0.2}
+    t["router"][4] = -5.0 * t["router"][0].abs()                       # expert 4 never wins ...
+    for e in range(E):
+        t[f"e{e}.up"] = (torch.randn(ff, W, generator=g, device=DEV) * 0.2).to(dtype)
+        t[f"e{e}.down"] = (torch.randn(W, ff, generator=g, device=DEV) * 0.2).to(dtype)
+    part.load(t)
+    x = (torch.randn(T, W, generator=g, device=DEV).abs() + 0.1).to(dtype)          # ... on inputs that are all positive
+    monkeypatch.setattr(RoutedMLP, "LIBRARY_ROWS", 1)
+    by_expert = part.forward(x).float().cpu()
+    monkeypatch.setattr(RoutedMLP, "LIBRARY_ROWS", 10 ** 9)
+    grouped = part.forward(x).float().cpu()
+    w = {f"p.{k}": v.float().cpu() for k, v in t.items()}
+    want = plain.routed_ff(x.float().cpu(), w, "p.", {"router": {"experts": E, "top": top}})
+    experts, _ = plain.route(x.float().cpu(), w["p.router"], top)
+    assert 4 not in experts.unique().tolist()
+    # (bfloat16: the plain model rounds neither the weighted input nor the activation; 3 % of the largest output)
+    t_ = dict(rtol=1e-4, atol=1e-4) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2 * float(want.abs().max()))
+    assert torch.allclose(grouped, want, **t_) and torch.allclose(by_expert, want, **t_)
+    assert torch.allclose(grouped, by_expert, **t_)

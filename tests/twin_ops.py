@@ -219,6 +219,13 @@ class TwinOps:
                 self.activation(tmp, y, act)
             out[a:b] = tmp.to(out.dtype)
 
+    def moe_gather(self, xs, x, order, row_scale, top):
+        pairs = order[: xs.shape[0]].long()
+        rows = x[pairs // top].float()
+        if row_scale is not None:
+            rows = rows * row_scale.reshape(-1)[pairs][:, None]
+        xs.copy_(rows.to(xs.dtype))
+
     def moe_combine(self, out, y, place, pair_weights, top):
         rows = y[place.long()].view(out.shape[0], top, -1)
         if pair_weights is not None:

@@ -3,7 +3,7 @@
 // count back to the host: every launch is sized for the worst case and blocks without work leave, so the
 // chain can sit in a captured graph.
 //
-//   ts_router_topk     z = Wr x in 32-bit (one warp a token, fixed summation order), score = sigmoid(z) or
+//   ts_router_topk     z = Wr x in 32-bit (one block a token, fixed summation order), score = sigmoid(z) or
 //                      softmax(z); the `top` largest by z (ties: the lower index); weights = their scores,
 //                      optionally divided by their sum.
 //   ts_moe_align       pairs p = t * top + r sorted by expert: offsets[E + 1], order[P] (sorted place -> pair),
@@ -24,24 +24,28 @@ namespace {
 constexpr int GL_BM = 64, GL_BN = 64, GL_BK = 16, GL_PAD = 4;
 
 // ---------------------------------------------------------------------------------------------------
+// One block of RT_THREADS a token: thread i owns the columns i, i + RT_THREADS, ... of the token's row and keeps one sum
+// per expert of a group of eight, so the loads of a step of the loop are all independent (the router's rows come
+// from memory once a step: a chain of dependent loads would cost a round trip each); the threads' sums are added
+// lane by lane, then warp by warp, in a fixed order.  Warp 0 then picks the experts.
+constexpr int RT_THREADS = 256;
+
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(RT_THREADS)
 router_topk_kernel(int* __restrict__ idx_out, float* __restrict__ w_out, const T* __restrict__ x,
                    const float* __restrict__ wr, int T_, int E, int K, int top, int softmax, int renorm) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float smem[];
+  float* z = smem;                       // [E]
+  float* part = smem + E;                // [RT_THREADS / 32][8]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * 4 + warp;
-  if (t >= T_) return;
-  float* z = smem + warp * E;
+  const int t = blockIdx.x;
   const T* xr = x + (size_t)t * K;
-  // eight experts at a time, each lane with eight independent sums: the router's rows are read once a step, from
-  // memory, and a chain of one load after the other would cost a memory round trip per 128 bytes
   for (int e0 = 0; e0 < E; e0 += 8) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-    for (int k = lane; k < K; k += 32) {
+#pragma unroll 2
+    for (int k = threadIdx.x; k < K; k += RT_THREADS) {
       const float xv = to_f(xr[k]);
 #pragma unroll
       for (int i = 0; i < 8; ++i)
@@ -50,9 +54,17 @@ router_topk_kernel(int* __restrict__ idx_out, float* __restrict__ w_out, const T
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const float v = warp_sum(acc[i]);
-      if (lane == 0 && e0 + i < E) z[e0 + i] = v;
+      if (lane == 0) part[warp * 8 + i] = v;
     }
+    __syncthreads();
+    if (threadIdx.x < 8 && e0 + threadIdx.x < E) {
+      float v = 0.f;
+      for (int w = 0; w < RT_THREADS / 32; ++w) v += part[w * 8 + threadIdx.x];
+      z[e0 + threadIdx.x] = v;
+    }
+    __syncthreads();
   }
+  if (warp != 0) return;
   __syncwarp();
   float zmax = -INFINITY, denom = 1.f;
   if (softmax) {
@@ -322,6 +334,103 @@ grouped_linear_mma_kernel(TO* __restrict__ out, const bf16* __restrict__ x, cons
     }
 }
 
+// The same product for steps of a few tokens, where an expert has a handful of rows and the time is the experts'
+// weights crossing from memory once: no shared memory, no barrier, and the arithmetic on the tensor cores so that the
+// instruction stream stays thin (an FFMA version spent 108 instructions a warp per 512 bytes of weights and was
+// bound by issue slots at a third of the memory bandwidth).  A warp owns EIGHT output columns of one row tile and up
+// to eight input rows at a time: per 32 columns of k, lane (g, t) loads 16 bytes of weight row n0 + g and 16 bytes of
+// input row g, both at k + 8 t, and feeds them to two m16n8k16 products.  (The products' k index is a permutation
+// of the real one, the same for both operands, so the sum is the same sum.)  GV_UNROLL steps of loads are in flight.
+// Rows 8..15 of the product are zero.  A tile with more rows is walked eight at a time.
+constexpr int GV_ROWS = 8, GV_WARPS = 8, GV_UNROLL = 8;
+constexpr int GV_STREAM_ROWS = 64;      // steps with at most this many (token, choice) pairs take this kernel
+
+template <typename TO>
+__global__ void __launch_bounds__(GV_WARPS * 32)
+grouped_linear_stream_kernel(TO* __restrict__ out, const bf16* __restrict__ x, const bf16* __restrict__ w,
+                             const int* __restrict__ order, const float* __restrict__ row_scale,
+                             const int* __restrict__ offsets, const int* __restrict__ tiles, int top, int N, int K, int act) {
+  pdl_launch_dependents();
+  // (the tile list is written by the kernel before this one: nothing can be fetched ahead of the wait)
+  pdl_wait();
+  if ((int)blockIdx.y >= tiles[0]) return;
+  const int e = tiles[1 + 2 * blockIdx.y], m0 = tiles[2 + 2 * blockIdx.y];
+  const int m_end = min(offsets[e + 1], m0 + GL_BM);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int n0 = (blockIdx.x * GV_WARPS + warp) * 8;
+  if (n0 >= N) return;
+  const bool n_ok = n0 + g < N;
+  const bf16* wrow = w + ((size_t)e * N + (n_ok ? n0 + g : n0)) * K + t * 8;
+  for (int r0 = m0; r0 < m_end; r0 += GV_ROWS) {
+    const int row = r0 + g;
+    const bool row_ok = row < m_end;
+    const bf16* xrow = x + t * 8;
+    float scale = 1.f;
+    if (row_ok) {
+      if (order != nullptr) {
+        const int p = order[row];
+        xrow += (size_t)(p / top) * K;
+        if (row_scale != nullptr) scale = row_scale[p];
+      } else {
+        xrow += (size_t)row * K;
+      }
+    }
+    const bool scaled = row_scale != nullptr && order != nullptr;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k0 = 0; k0 < K; k0 += 32 * GV_UNROLL) {
+      uint4 wv[GV_UNROLL], xv[GV_UNROLL];
+#pragma unroll
+      for (int u = 0; u < GV_UNROLL; ++u) {
+        const int k = k0 + u * 32;
+        const bool k_ok = k + t * 8 < K;
+        wv[u] = (k_ok && n_ok) ? __ldcs(reinterpret_cast<const uint4*>(wrow + k)) : make_uint4(0u, 0u, 0u, 0u);
+        xv[u] = (k_ok && row_ok) ? *reinterpret_cast<const uint4*>(xrow + k) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < GV_UNROLL; ++u) {
+        if (scaled) {
+          __nv_bfloat162* x2 = reinterpret_cast<__nv_bfloat162*>(&xv[u]);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(x2[i]);
+            x2[i] = __floats2bfloat162_rn(f.x * scale, f.y * scale);
+          }
+        }
+        const unsigned a1[4] = {xv[u].x, 0u, xv[u].y, 0u};
+        const unsigned a2[4] = {xv[u].z, 0u, xv[u].w, 0u};
+        mma_bf16(acc, a1, wv[u].x, wv[u].y);
+        mma_bf16(acc, a2, wv[u].z, wv[u].w);
+      }
+    }
+    if (row_ok) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int n = n0 + 2 * t + i;
+        if (n < N) out[(size_t)row * N + n] = from_f<TO>(ts_activate(acc[i], act));
+      }
+    }
+  }
+}
+
+// xs[i, :] = x[order[i] / top, :] (* row_scale[order[i]], rounded to the storage type): the experts' input rows in
+// sorted order, for the path that hands each expert's rows to a many-row product of its own.
+template <typename T>
+__global__ void moe_gather_kernel(T* __restrict__ xs, const T* __restrict__ x, const int* __restrict__ order,
+                                  const float* __restrict__ row_scale, int top, int K) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int p = order[blockIdx.x];
+  const T* src = x + (size_t)(p / top) * K;
+  T* dst = xs + (size_t)blockIdx.x * K;
+  if (row_scale != nullptr) {
+    const float sc = row_scale[p];
+    for (int k = threadIdx.x; k < K; k += blockDim.x) dst[k] = from_f<T>(to_f(src[k]) * sc);
+  } else {
+    for (int k = threadIdx.x; k < K; k += blockDim.x) dst[k] = src[k];
+  }
+}
+
 template <typename T>
 __global__ void moe_combine_kernel(T* __restrict__ out, const float* __restrict__ y, const int* __restrict__ place,
                                    const float* __restrict__ pair_w, int top, int N) {
@@ -350,12 +459,12 @@ TS_API int ts_router_topk(int* idx_out, float* w_out, const void* x, const float
   if (E <= 0 || top <= 0 || top > E) TS_REFUSE(TS_ERR_SHAPE, "ts_router_topk: top %d of %d experts", top, E);
   if (E > 2048) TS_REFUSE(TS_ERR_LIMIT, "ts_router_topk: %d experts (limit 2048)", E);
   cudaStream_t s = (cudaStream_t)stream;
-  const size_t smem = sizeof(float) * 4 * E;
+  const size_t smem = sizeof(float) * (E + RT_THREADS / 32 * 8);
   if (dtype == TS_F32)
-    ts_launch(router_topk_kernel<float>, dim3(ceil_div(T, 4)), dim3(128), smem, s, idx_out, w_out, (const float*)x, wr, T,
+    ts_launch(router_topk_kernel<float>, dim3(T), dim3(RT_THREADS), smem, s, idx_out, w_out, (const float*)x, wr, T,
               E, K, top, softmax, renorm);
   else if (dtype == TS_BF16)
-    ts_launch(router_topk_kernel<bf16>, dim3(ceil_div(T, 4)), dim3(128), smem, s, idx_out, w_out, (const bf16*)x, wr, T,
+    ts_launch(router_topk_kernel<bf16>, dim3(T), dim3(RT_THREADS), smem, s, idx_out, w_out, (const bf16*)x, wr, T,
               E, K, top, softmax, renorm);
   else
     TS_REFUSE(TS_ERR_DTYPE, "ts_router_topk: dtype %d", dtype);
@@ -371,6 +480,20 @@ TS_API int ts_moe_align(const int* idx, int P, int E, int* offsets, int* order, 
   TS_LAUNCH_CHECK();
 }
 
+
+TS_API int ts_moe_gather(void* xs, const void* x, const int* order, const float* row_scale, int P, int top, int K, int dtype,
+                         void* stream) {
+  if (P <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == TS_F32)
+    ts_launch(moe_gather_kernel<float>, dim3(P), dim3(256), 0, s, (float*)xs, (const float*)x, order, row_scale, top, K);
+  else if (dtype == TS_BF16)
+    ts_launch(moe_gather_kernel<bf16>, dim3(P), dim3(256), 0, s, (bf16*)xs, (const bf16*)x, order, row_scale, top, K);
+  else
+    TS_REFUSE(TS_ERR_DTYPE, "ts_moe_gather: dtype %d", dtype);
+  TS_LAUNCH_CHECK();
+}
+
 // w: [E, N, K].  out: [P, N].  act: 0 none, 1 tanh-form GELU, 2 squared ReLU, 3 SiLU.
 TS_API int ts_grouped_linear(void* out, const void* x, const void* w, const int* order, const float* row_scale,
                              const int* offsets, const int* tiles, int P, int E, int top, int N, int K, int act,
@@ -380,6 +503,18 @@ TS_API int ts_grouped_linear(void* out, const void* x, const void* w, const int*
   cudaStream_t s = (cudaStream_t)stream;
   dim3 grid(ceil_div(N, GL_BN), ceil_div(P, GL_BM) + E);
   if (grid.y > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_grouped_linear: %d rows too many for one launch", P);
+  if (dtype == TS_BF16 && K % 8 == 0 && !(((uintptr_t)x | (uintptr_t)w) & 15) && P <= GV_STREAM_ROWS) {
+    dim3 sgrid(ceil_div(N, GV_WARPS * 8), ceil_div(P, GL_BM) + E);
+    if (out_dtype == TS_BF16)
+      ts_launch(grouped_linear_stream_kernel<bf16>, dim3(sgrid), dim3(GV_WARPS * 32), 0, s, (bf16*)out, (const bf16*)x,
+                (const bf16*)w, order, row_scale, offsets, tiles, top, N, K, act);
+    else if (out_dtype == TS_F32)
+      ts_launch(grouped_linear_stream_kernel<float>, dim3(sgrid), dim3(GV_WARPS * 32), 0, s, (float*)out, (const bf16*)x,
+                (const bf16*)w, order, row_scale, offsets, tiles, top, N, K, act);
+    else
+      TS_REFUSE(TS_ERR_DTYPE, "ts_grouped_linear: dtype %d -> %d", dtype, out_dtype);
+    TS_LAUNCH_CHECK();
+  }
   if (dtype == TS_BF16 && K % 8 == 0 && !(((uintptr_t)x | (uintptr_t)w) & 15)) {
     const size_t smem = (size_t)GM_STAGES * (GM_BM + GM_BN) * GM_BK * 2;
     static bool configured = false;

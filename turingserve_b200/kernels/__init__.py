@@ -119,6 +119,7 @@ class CudaOps:
             "ts_moe_align": [P, I, I, P, P, P, P, P],
             "ts_grouped_linear": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
             "ts_moe_combine": [P, P, P, P, I, I, I, I, P],
+            "ts_moe_gather": [P, P, P, P, I, I, I, I, P],
         }
         for name, args in sigs.items():
             fn = getattr(self.lib, name)
@@ -646,6 +647,13 @@ class CudaOps:
         self._check(self.lib.ts_grouped_linear(_ptr(out), _ptr(x), _ptr(w), _ptr(order), _ptr(row_scale), _ptr(offsets),
                                                _ptr(tiles), P, E, top, N, K, self.ACTIVATIONS[act], _code(x.dtype),
                                                _code(out.dtype), self._stream()), "grouped_linear")
+
+    def moe_gather(self, xs, x, order, row_scale, top: int) -> None:
+        """xs[i] = x[order[i] // top] (times row_scale[order[i]], rounded to x's type): the experts' input rows
+        in sorted order."""
+        P, K = xs.shape
+        self._check(self.lib.ts_moe_gather(_ptr(xs), _ptr(x), _ptr(order), _ptr(row_scale), P, top, K, _code(x.dtype),
+                                           self._stream()), "moe_gather")
 
     def moe_combine(self, out, y, place, pair_weights, top: int) -> None:
         """out[t] = sum over a token's choices r of (pair_weights[t, r] *) y[place[t top + r]] (y float32)."""

@@ -6,6 +6,10 @@ two products run over the sorted groups; the chosen score multiplies the expert'
 "input", the product reads score * x rounded to the engine's type) or its output; a token's choices are
 summed in 32-bit in the order of their rank.  No count comes back to the host, so the chain may sit in a
 captured step.  The experts' weights are stacked [E, ff, hidden] and [E, hidden, ff] when they arrive.
+
+Many rows (``LIBRARY_ROWS`` pairs or more, outside a capture): the group sizes are read back once, the input
+rows are gathered in sorted order, and every expert's rows go through ``ops().linear`` as a product of their own,
+i.e. to the many-row kernels and the vendor library that the dense products of such steps use.
 """
 
 from __future__ import annotations
@@ -18,6 +22,10 @@ from turingserve_b200.parts.mlp import ACTIVATIONS
 
 
 class RoutedMLP(FeedForward):
+    # from this many (token, choice) pairs in a step the experts' products are launched one by one (2,048 tokens of
+    # width 3,584 through 8 experts of 7,104: 2.7 ms for the two grouped products, 0.5 ms this way)
+    LIBRARY_ROWS = 1024
+
     def __init__(self, spec, ctx: BuildContext) -> None:
         self.hidden = ctx.hidden_size
         self.E, self.top, self.inter = int(spec.num_experts), int(spec.top_k), int(spec.intermediate_size)
@@ -51,10 +59,24 @@ class RoutedMLP(FeedForward):
         ops.router_topk(idx, weights, x, self.w_router, self.softmax, self.renormalize)
         offsets, order, place, tiles = ops.moe_align(idx, self.E)
         a = torch.empty((T * top, self.inter), dtype=x.dtype, device=x.device)
-        ops.grouped_linear(a, x, self.w_up, order, weights if self.on_input else None, offsets, tiles, top,
-                           self.activation)
         y = torch.empty((T * top, self.hidden), dtype=torch.float32, device=x.device)
-        ops.grouped_linear(y, a, self.w_down, None, None, offsets, tiles, 1)
+        # the experts' input rows in sorted order, weighted and rounded once (the products then read plain rows)
+        xs = torch.empty((T * top, self.hidden), dtype=x.dtype, device=x.device)
+        ops.moe_gather(xs, x, order, weights if self.on_input else None, top)
+        if T * top >= self.LIBRARY_ROWS and x.is_cuda and not torch.cuda.is_current_stream_capturing():
+            bounds = offsets[: self.E + 1].tolist()                      # the one read-back of this path
+            for e in range(self.E):
+                lo, hi = bounds[e], bounds[e + 1]
+                if hi > lo:
+                    ops.linear(a[lo:hi], xs[lo:hi], self.w_up[e])
+            ops.activation(a, a, self.activation)
+            for e in range(self.E):
+                lo, hi = bounds[e], bounds[e + 1]
+                if hi > lo:
+                    ops.linear(y[lo:hi], a[lo:hi], self.w_down[e])
+        else:
+            ops.grouped_linear(a, xs, self.w_up, None, None, offsets, tiles, 1, self.activation)
+            ops.grouped_linear(y, a, self.w_down, None, None, offsets, tiles, 1)
         out = torch.empty((T, self.hidden), dtype=x.dtype, device=x.device)
         ops.moe_combine(out, y, place, None if self.on_input else weights, top)
         return out
