@@ -100,10 +100,12 @@ def plain_lightning(proj, decay, H, D, V, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,D,V", [(3, 8, 24), (2, 48, 16), (1, 64, 40), (2, 256, 256)])
+@pytest.mark.parametrize("H,D,V", [(3, 8, 24), (2, 48, 16), (1, 64, 40), (2, 256, 256), (2, 12, 20), (3, 5, 33)])
 def test_state_scan_whole_in_portions_and_token_by_token(ops, dtype, H, D, V):
     """The same tokens as one portion, as portions down to two tokens and one, and one by one: the same
-    outputs and the same state; two requests in one launch with slots that are not their batch rows."""
+    outputs and the same state; two requests in one launch with slots that are not their batch rows.  Sizes
+    that are multiples of 8 (rows fetched by 16-byte asynchronous copies), sizes that are not (plain loads), a
+    state of 256 x 256 (32 row parts a block)."""
     g = torch.Generator(device=DEV).manual_seed(D + V)
     T = 37
     decay = torch.tensor([0.6, 0.97, 1.0][:H], device=DEV)

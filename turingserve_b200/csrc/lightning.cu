@@ -77,6 +77,7 @@ lightning_kernel(float* __restrict__ out, const T* __restrict__ proj, int proj_s
       }
     }
   };
+  for (int i = threadIdx.x; i < 2 * LT_GROUP * Dp; i += blockDim.x) q_s[i] = 0.f;      // (q_s and k_s: rows beyond D stay zero)
   fetch(0, 0);
   cp_async_commit();
   int buf = 0;
@@ -86,24 +87,25 @@ lightning_kernel(float* __restrict__ out, const T* __restrict__ proj, int proj_s
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();                                       // this group's raw rows are here; the group before is stored
-    for (int i = threadIdx.x; i < gn * Dp; i += blockDim.x) {
-      const int r = i / Dp, d = i % Dp;
-      float qv = 0.f, kv = 0.f;
-      if (d < D) {
-        if (fast_rows) {
-          const T* src = raw + ((size_t)buf * LT_GROUP + r) * raw_row;
-          qv = to_f(src[d]);
-          kv = to_f(src[D + d]);
-        } else {
-          const T* row = proj + (size_t)(t0 + g0 + r) * proj_stride;
-          qv = to_f(row[q_off + d]);
-          kv = to_f(row[k_off + d]);
-        }
-        qv = act_silu<T>(qv);
-        kv = act_silu<T>(kv);
+    if (fast_rows) {
+      // 16 bytes (PER16 values) of q or k at a time: the index arithmetic once a piece, not once a value
+      const int chunks = D / PER16;
+      for (int i = threadIdx.x; i < gn * 2 * chunks; i += blockDim.x) {
+        const int r = i / (2 * chunks), c = i % (2 * chunks);
+        const int which = c >= chunks, cc = (which ? c - chunks : c) * PER16;
+        const uint4 rawv = *reinterpret_cast<const uint4*>(raw + ((size_t)buf * LT_GROUP + r) * raw_row + which * D + cc);
+        const T* e = reinterpret_cast<const T*>(&rawv);
+        float* dst = (which ? k_s : q_s) + r * Dp + cc;
+#pragma unroll
+        for (int u = 0; u < PER16; ++u) dst[u] = act_silu<T>(to_f(e[u]));
       }
-      q_s[i] = qv;
-      k_s[i] = kv;
+    } else {
+      for (int i = threadIdx.x; i < gn * D; i += blockDim.x) {
+        const int r = i / D, d = i % D;
+        const T* row = proj + (size_t)(t0 + g0 + r) * proj_stride;
+        q_s[r * Dp + d] = act_silu<T>(to_f(row[q_off + d]));
+        k_s[r * Dp + d] = act_silu<T>(to_f(row[k_off + d]));
+      }
     }
     for (int i = threadIdx.x; i < gn * LT_COLS; i += blockDim.x) {
       const int r = i / LT_COLS, c = i % LT_COLS;
@@ -120,20 +122,20 @@ lightning_kernel(float* __restrict__ out, const T* __restrict__ proj, int proj_s
       const float vj = v_s[r * LT_COLS + col];
       const float4* qr = reinterpret_cast<const float4*>(q_s + r * Dp + part * LT_ROWS);
       const float4* kr = reinterpret_cast<const float4*>(k_s + r * Dp + part * LT_ROWS);
-      float o = 0.f;
+      float o = 0.f, o2 = 0.f;                                 // two chains of four instead of one of eight
 #pragma unroll
       for (int i = 0; i < LT_ROWS / 4; ++i) {
         const float4 k4 = kr[i], q4 = qr[i];
         s[4 * i + 0] = fmaf(lam, s[4 * i + 0], k4.x * vj);
         o = fmaf(s[4 * i + 0], q4.x, o);
         s[4 * i + 1] = fmaf(lam, s[4 * i + 1], k4.y * vj);
-        o = fmaf(s[4 * i + 1], q4.y, o);
+        o2 = fmaf(s[4 * i + 1], q4.y, o2);
         s[4 * i + 2] = fmaf(lam, s[4 * i + 2], k4.z * vj);
         o = fmaf(s[4 * i + 2], q4.z, o);
         s[4 * i + 3] = fmaf(lam, s[4 * i + 3], k4.w * vj);
-        o = fmaf(s[4 * i + 3], q4.w, o);
+        o2 = fmaf(s[4 * i + 3], q4.w, o2);
       }
-      o_s[(r * parts + part) * LT_COLS + col] = o;
+      o_s[(r * parts + part) * LT_COLS + col] = o + o2;
     }
     __syncthreads();
     for (int i = threadIdx.x; i < gn * LT_COLS; i += blockDim.x) {
