@@ -63,6 +63,11 @@ TINY = {
         {**_light(2, 128, 64, [0.97, 0.999]), "mlp": _moe(8, 2, 128)},
         {**_attn(2, 2, 32, 64, 0.4, 0.18), "mlp": None},
     ]), 14, 64),
+    # no attention layer at all: the engine runs without a single cache group, on state slots alone
+    "Z": (dict(width=32, vocab=50, eps=1e-5, layers=[
+        {**_light(2, 8, 8, [0.9, 0.95]), "mlp": None},
+        {**_light(1, 16, 8, [0.99]), "mlp": _dense(40)},
+    ]), 15, 16),
 }
 
 # how much larger than the base deviation a tensor's entries are (by the end of its name): queries and keys

@@ -99,7 +99,7 @@ def _replay_cpu(folder, name, steps):
     return schedules.collect(steps, outs)
 
 
-@pytest.mark.parametrize("name", ["P", "Q", "R"])
+@pytest.mark.parametrize("name", ["P", "Q", "R", "Z"])
 @pytest.mark.parametrize("schedule", ["decode_tail", "portions", "mixed"])
 def test_host_logic_against_plain(tmp_path, name, schedule):
     """More requests than state slots, a pool that makes pages go round, portions down to two tokens."""
