@@ -26,6 +26,7 @@ constexpr int DM_WARPS = 4;
 constexpr int DM_ROWS = DM_WARPS * 16;
 constexpr int DM_TILE = 64;
 constexpr int DM_STAGES = 3;
+constexpr int DM_SPLIT_TILES = 4;         // fewest 64-key tiles a piece of a decoding request's keys holds
 constexpr int DM_PAGES_S = 2048;          // block-table entries a block keeps in shared memory
 constexpr float DM_LOG2E = 1.4426950408889634f;
 
@@ -56,7 +57,8 @@ attention_diff_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ proj,
   int nsplit = 1;
   if (split && n_rows > 0 && scratch != nullptr) {
     const int all_tiles = seq_len > 0 ? (prefix + (n_rows - 1) / G) / DM_TILE + 1 : 0;
-    nsplit = max(1, min(min((int)gridDim.x, max_splits), all_tiles));
+    // at least DM_SPLIT_TILES tiles a piece: every piece is one more partial result for the last block to fold
+    nsplit = max(1, min(min((int)gridDim.x, max_splits), (all_tiles + DM_SPLIT_TILES - 1) / DM_SPLIT_TILES));
   }
   if ((int)blockIdx.x >= (split ? nsplit : n_row_tiles)) return;
   const int row0 = split ? 0 : (n_row_tiles - 1 - blockIdx.x) * DM_ROWS;      // longest tiles first
