@@ -39,7 +39,8 @@ __global__ void rmsnorm_wide_kernel(T* __restrict__ out, float* __restrict__ str
 template <typename T, typename WT, int CH>
 __global__ void __launch_bounds__(256)
 rmsnorm_wide_vec_kernel(T* __restrict__ out, float* __restrict__ stream, const T* __restrict__ add1,
-                        const T* __restrict__ add2, const WT* __restrict__ w, float eps, int hidden, int first) {
+                        const T* __restrict__ add2, const WT* __restrict__ w, float eps, int hidden, int first,
+                        const float* __restrict__ part, int splits, size_t split_stride, const T* __restrict__ bias) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float scratch[32];
@@ -52,6 +53,18 @@ rmsnorm_wide_vec_kernel(T* __restrict__ out, float* __restrict__ stream, const T
     if (i < hidden) {
       float4 s4 = first ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(stream + base + i);
       v[c][0] = s4.x; v[c][1] = s4.y; v[c][2] = s4.z; v[c][3] = s4.w;
+      if (part != nullptr) {
+        // a product left unreduced by its kernel: the partial sums in split order, the bias, and the rounding the
+        // product's own epilogue would have done
+        float4 p4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int sp = 0; sp < splits; ++sp) {
+          const float4 q4 = __ldcg(reinterpret_cast<const float4*>(part + (size_t)sp * split_stride + base + i));
+          p4.x += q4.x; p4.y += q4.y; p4.z += q4.z; p4.w += q4.w;
+        }
+        const float pv[4] = {p4.x, p4.y, p4.z, p4.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[c][k] += round_to<T>(pv[k] + (bias != nullptr ? to_f(bias[i + k]) : 0.f));
+      }
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         if (add1 != nullptr) v[c][k] += to_f(add1[base + i + k]);
@@ -101,14 +114,36 @@ __global__ void activation_kernel(T* __restrict__ out, const T* __restrict__ x, 
     out[i] = from_f<T>(ts_activate(to_f(x[i]), kind));
 }
 
+// out = act(T(sum over splits of part + bias)): the activation fed by a product left unreduced
+template <typename T>
+__global__ void activation_parts_kernel(T* __restrict__ out, const float* __restrict__ part, int splits, size_t split_stride,
+                                        const T* __restrict__ bias, size_t n, int cols, int kind) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float v = 0.f;
+    for (int sp = 0; sp < splits; ++sp) v += __ldcg(part + (size_t)sp * split_stride + i);
+    if (bias != nullptr) v += to_f(bias[i % cols]);
+    out[i] = from_f<T>(ts_activate(round_to<T>(v), kind));
+  }
+}
+
 int threads_for(int n) { return n >= 2048 ? 512 : (n >= 512 ? 256 : 128); }
 
 }  // namespace
 
+// The rows a multiple of 4 long and at most 4,096 (ts_rmsnorm_wide_takes_parts) may also take a product left
+// unreduced: part [splits, T, hidden] 32-bit partial sums (+ bias), added to the stream after the rounding the
+// product's epilogue would have done.
+TS_API int ts_rmsnorm_wide_takes_parts(int hidden) { return hidden % 4 == 0 && hidden <= 4 * 4 * 256; }
+
 TS_API int ts_rmsnorm_wide(void* out, float* stream, const void* add1, const void* add2, const void* w, float eps,
-                           int T, int hidden, int first, int dtype, int w_dtype, void* stream_) {
+                           int T, int hidden, int first, int dtype, int w_dtype, const float* part, int splits,
+                           const void* bias, void* stream_) {
   if (T <= 0) return 0;
-  if (first && add1 == nullptr) TS_REFUSE(TS_ERR_SHAPE, "ts_rmsnorm_wide: a stream starts from a tensor");
+  if (first && add1 == nullptr && part == nullptr) TS_REFUSE(TS_ERR_SHAPE, "ts_rmsnorm_wide: a stream starts from a tensor");
+  if (part != nullptr && (!ts_rmsnorm_wide_takes_parts(hidden) || ((uintptr_t)stream & 15) || ((uintptr_t)part & 15)))
+    TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_rmsnorm_wide: partial sums with rows of %d", hidden);
   cudaStream_t s = (cudaStream_t)stream_;
   const int th = threads_for(hidden);
   if (hidden % 4 == 0 && hidden <= 4 * 4 * 256 && !((uintptr_t)stream & 15)) {
@@ -116,7 +151,7 @@ TS_API int ts_rmsnorm_wide(void* out, float* stream, const void* add1, const voi
     const int tv = ((hidden / 4 + ch - 1) / ch + 31) / 32 * 32;
 #define TS_WV(TT, WT, CH)                                                                                           \
   ts_launch(rmsnorm_wide_vec_kernel<TT, WT, CH>, dim3(T), dim3(tv), 0, s, (TT*)out, stream, (const TT*)add1, (const TT*)add2, \
-            (const WT*)w, eps, hidden, first)
+            (const WT*)w, eps, hidden, first, part, splits, (size_t)T * hidden, (const TT*)bias)
 #define TS_WVC(TT, WT)      \
   do {                      \
     if (ch == 1) TS_WV(TT, WT, 1); \
@@ -155,6 +190,25 @@ TS_API int ts_gated_rmsnorm(void* out, const float* x, const void* gate, int gat
   else if (dtype == TS_BF16 && w_dtype == TS_F32) TS_GN(bf16, float);
   else TS_REFUSE(TS_ERR_DTYPE, "ts_gated_rmsnorm: dtype %d with scale dtype %d", dtype, w_dtype);
 #undef TS_GN
+  TS_LAUNCH_CHECK();
+}
+
+// part: [splits, rows, cols] 32-bit partial sums of a product; out [rows, cols].
+TS_API int ts_activation_parts(void* out, const float* part, int splits, const void* bias, int rows, int cols, int kind,
+                               int dtype, void* stream) {
+  const size_t n = (size_t)rows * cols;
+  if (n == 0) return 0;
+  if (kind < 1 || kind > 3) TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_activation_parts: kind %d", kind);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+  if (dtype == TS_F32)
+    ts_launch(activation_parts_kernel<float>, dim3(blocks), dim3(256), 0, s, (float*)out, part, splits, n, (const float*)bias,
+              n, cols, kind);
+  else if (dtype == TS_BF16)
+    ts_launch(activation_parts_kernel<bf16>, dim3(blocks), dim3(256), 0, s, (bf16*)out, part, splits, n, (const bf16*)bias, n,
+              cols, kind);
+  else
+    TS_REFUSE(TS_ERR_DTYPE, "ts_activation_parts: dtype %d", dtype);
   TS_LAUNCH_CHECK();
 }
 

@@ -108,7 +108,8 @@ class CudaOps:
             "ts_decode_step": [P, I, I, P],
             "ts_decode_step_encode_map": [P, P, I, I],
             "ts_poke_status": [I, I, P],
-            "ts_rmsnorm_wide": [P, P, P, P, P, F, I, I, I, I, I, P],
+            "ts_rmsnorm_wide": [P, P, P, P, P, F, I, I, I, I, I, P, I, P, P],
+            "ts_activation_parts": [P, P, I, P, I, I, I, I, P],
             "ts_gated_rmsnorm": [P, P, P, I, P, F, I, I, I, I, P],
             "ts_activation": [P, P, ctypes.c_longlong, I, I, P],
             "ts_lightning": [P, P, I, P, P, P, P, I, I, I, I, I, P],
@@ -129,6 +130,8 @@ class CudaOps:
         self.lib.ts_attention_diff_mma_supported.restype = c_int
         self.lib.ts_attention_diff_mma_scratch_floats.argtypes = [I, I, I, I]
         self.lib.ts_attention_diff_mma_scratch_floats.restype = ctypes.c_longlong
+        self.lib.ts_rmsnorm_wide_takes_parts.argtypes = [I]
+        self.lib.ts_rmsnorm_wide_takes_parts.restype = c_int
         self.lib.ts_moe_tile_rows.argtypes = []
         self.lib.ts_moe_tile_rows.restype = c_int
         self.lib.ts_attention_decode_supported.argtypes = [I, I, I, I]
@@ -543,11 +546,19 @@ class CudaOps:
         from them instead); out = stream / sqrt(mean(stream^2) + eps) * weight, 32-bit, rounded once.
         ``out`` None: only the sum."""
         T, h = stream.shape
+        part, splits, bias = None, 0, None
+        if isinstance(add1, (LazyProduct, Deferred)) and self.lib.ts_rmsnorm_wide_takes_parts(h):
+            # a few-token product that was put off: its partial sums are summed here, no kernel of their own
+            add1 = self._settle(add1)
+            if isinstance(add1, Deferred) and add1.part.data_ptr() % 16 == 0 and stream.data_ptr() % 16 == 0:
+                part, splits, bias, dt = add1.part, add1.splits, add1.bias, add1.dtype
+                add1 = None
         add1, add2 = self.materialize(add1), self.materialize(add2)
-        dt = add1.dtype if add1 is not None else (add2.dtype if add2 is not None else out.dtype)
+        if part is None:
+            dt = add1.dtype if add1 is not None else (add2.dtype if add2 is not None else out.dtype)
         self._check(self.lib.ts_rmsnorm_wide(_ptr(out), _ptr(stream), _ptr(add1), _ptr(add2), _ptr(weight), float(eps),
-                                             T, h, 1 if first else 0, _code(dt), _code(weight.dtype), self._stream()),
-                    "rmsnorm_stream")
+                                             T, h, 1 if first else 0, _code(dt), _code(weight.dtype), _ptr(part), splits,
+                                             _ptr(bias), self._stream()), "rmsnorm_stream")
 
     def gated_rmsnorm(self, out, x, gate, weight, eps: float) -> None:
         """out = x / sqrt(mean(x^2) + eps) * weight * sigmoid(gate), x float32 [T, n]; ``gate`` [T, n] in
@@ -563,7 +574,15 @@ class CudaOps:
     ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "relu2": 2, "silu": 3}
 
     def activation(self, out, x, kind: str) -> None:
-        """out = act(x) elementwise (32-bit arithmetic, one rounding); out may be x."""
+        """out = act(x) elementwise (32-bit arithmetic, one rounding); out may be x.  ``x`` may be a product that
+        was put off: its partial sums are summed on the way."""
+        x = self._settle(x)
+        if isinstance(x, Deferred):
+            rows, cols = x.shape
+            self._check(self.lib.ts_activation_parts(_ptr(out), _ptr(x.part), x.splits, _ptr(x.bias), rows, cols,
+                                                     self.ACTIVATIONS[kind], _code(out.dtype), self._stream()),
+                        "activation_parts")
+            return
         self._check(self.lib.ts_activation(_ptr(out), _ptr(x), x.numel(), self.ACTIVATIONS[kind], _code(x.dtype),
                                            self._stream()), "activation")
 

@@ -73,7 +73,7 @@ class DiffAttention(Mixer):
         ops.attention_diff(attn, proj, cache.k, cache.v, grp.block_tables, step, self.H, self.G, self.D, self.V,
                            cache.page_size, self.scale, self.lam, self.eps, 1.0 - self.diff)
         out = torch.empty((T, self.hidden), dtype=x.dtype, device=x.device)
-        return ops.linear(out, attn, self.w_o, self.b_o)
+        return ops.linear(out, attn, self.w_o, self.b_o, may_defer=True)
 
 
 register("mixer", "diff_attention", DiffAttention)

@@ -56,7 +56,7 @@ class Lightning(Mixer):
         y = torch.empty((T, hv), dtype=x.dtype, device=x.device)
         ops.gated_rmsnorm(y, o, proj[:, 2 * hd + hv:], self.norm_w, self.eps)
         out = torch.empty((T, self.hidden), dtype=x.dtype, device=x.device)
-        return ops.linear(out, y, self.w_o)
+        return ops.linear(out, y, self.w_o, may_defer=True)
 
 
 register("mixer", "lightning", Lightning)

@@ -29,10 +29,9 @@ class MLP(FeedForward):
         ops = kernels.ops()
         T = x.shape[0]
         a = torch.empty((T, self.inter), dtype=x.dtype, device=x.device)
-        ops.linear(a, x, self.w_up)
-        ops.activation(a, a, self.activation)
+        ops.activation(a, ops.linear(a, x, self.w_up, may_defer=True), self.activation)
         out = torch.empty((T, self.hidden), dtype=x.dtype, device=x.device)
-        return ops.linear(out, a, self.w_down)
+        return ops.linear(out, a, self.w_down, may_defer=True)
 
 
 register("feed_forward", "mlp", MLP)
