@@ -30,7 +30,7 @@ constexpr int DM_SPLIT_TILES = 4;         // fewest 64-key tiles a piece of a de
 constexpr int DM_PAGES_S = 2048;          // block-table entries a block keeps in shared memory
 constexpr float DM_LOG2E = 1.4426950408889634f;
 
-template <int D, int V>
+template <int D, int V, bool SPLIT>
 __global__ void __launch_bounds__(DM_WARPS * 32)
 attention_diff_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ proj, int proj_stride,
                           const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
@@ -51,7 +51,12 @@ attention_diff_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ proj,
   const int seq_len = seq_lens[b];
   const int n_rows = q_len * G;
   const int n_row_tiles = (n_rows + DM_ROWS - 1) / DM_ROWS;
-  const bool split = n_rows <= 16;                                   // every warp works for rows 0..15
+  // Two instances share a launch's requests: SPLIT takes those whose rows fit one warp (every warp then works for
+  // rows 0..15 on its own 16 keys of every tile, with loops a quarter as long at compile time), the other the rest.
+  constexpr bool split = SPLIT;
+  if ((n_rows <= 16) != SPLIT) return;
+  constexpr int NP = SPLIT ? 1 : DM_TILE / 16;                        // 16-key blocks of a tile a warp computes
+  const int key0 = SPLIT ? (int)(threadIdx.x >> 5) * 16 : 0;          // where they start
   const int prefix = seq_len - q_len;
   // a split request: the grid's x index is the piece of its keys; a portion: its row tile
   int nsplit = 1;
@@ -169,16 +174,15 @@ attention_diff_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ proj,
       const bool need_mask = (j0 + DM_TILE - 1 > w_pos_lo) || (j0 + DM_TILE - 1 > j_hi);
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        float s_acc[DM_TILE / 8][4];
+        float s_acc[2 * NP][4];
 #pragma unroll
-        for (int nt = 0; nt < DM_TILE / 8; ++nt) s_acc[nt][0] = s_acc[nt][1] = s_acc[nt][2] = s_acc[nt][3] = 0.f;
+        for (int nt = 0; nt < 2 * NP; ++nt) s_acc[nt][0] = s_acc[nt][1] = s_acc[nt][2] = s_acc[nt][3] = 0.f;
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
 #pragma unroll
-          for (int np = 0; np < DM_TILE / 16; ++np) {
-            if (split && np != warp) continue;                       // (warp-uniform) this warp's 16 keys only
+          for (int np = 0; np < NP; ++np) {
             const int mat = lane >> 3, r = lane & 7;
-            const int key = np * 16 + (mat >> 1) * 8 + r;
+            const int key = key0 + np * 16 + (mat >> 1) * 8 + r;
             const int ch = c * (D / 8) + ks * 2 + (mat & 1);
             unsigned b0, b1, b2, b3;
             ldmatrix_x4(b0, b1, b2, b3, ks_ + swz<DK>(key, ch));
@@ -188,13 +192,12 @@ attention_diff_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ proj,
         }
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int nt = 0; nt < DM_TILE / 8; ++nt) {
-          if (split && (nt >> 1) != warp) continue;                // another warp's keys: not computed, not used
+        for (int nt = 0; nt < 2 * NP; ++nt) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             float v = s_acc[nt][e] * sc;
             if (need_mask) {
-              const int j = j0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+              const int j = j0 + key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
               v = (j <= pos[e >> 1]) ? v : -INFINITY;
             }
             s_acc[nt][e] = v;
@@ -213,8 +216,7 @@ attention_diff_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ proj,
         }
         float rs[2] = {0.f, 0.f};
 #pragma unroll
-        for (int nt = 0; nt < DM_TILE / 8; ++nt) {
-          if (split && (nt >> 1) != warp) continue;
+        for (int nt = 0; nt < 2 * NP; ++nt) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const float p = exp2f(s_acc[nt][e] - m_use[e >> 1]);
@@ -236,8 +238,7 @@ attention_diff_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ proj,
           o[c][i][3] *= corr[1];
         }
 #pragma unroll
-        for (int kk = 0; kk < DM_TILE / 16; ++kk) {
-          if (split && kk != warp) continue;
+        for (int kk = 0; kk < NP; ++kk) {
           unsigned pf[4];
           pf[0] = pack_bf16(s_acc[2 * kk][0], s_acc[2 * kk][1]);
           pf[1] = pack_bf16(s_acc[2 * kk][2], s_acc[2 * kk][3]);
@@ -246,7 +247,7 @@ attention_diff_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ proj,
 #pragma unroll
           for (int i = 0; i < NT; i += 2) {
             const int mat = lane >> 3, r = lane & 7;
-            const int key = kk * 16 + (mat & 1) * 8 + r;
+            const int key = key0 + kk * 16 + (mat & 1) * 8 + r;
             const int ch = i + (mat >> 1);
             unsigned b0, b1, b2, b3;
             ldmatrix_x4_trans(b0, b1, b2, b3, vs_ + swz<V>(key, ch));
@@ -393,22 +394,34 @@ template <int D, int V>
 int launch_diff_mma(bf16* out, const bf16* proj, int proj_stride, const bf16* k_cache, const bf16* v_cache,
                     const int* block_tables, const int* q_start, const int* seq_lens, int B, int table_width,
                     int max_q_len, int H, int KVH, int page, float scale, float lambda, float eps, float out_scale,
-                    float* scratch, int* counters, int max_splits, cudaStream_t s) {
+                    float* scratch, int* counters, int max_splits, int kinds, cudaStream_t s) {
   const size_t tiles = (size_t)DM_STAGES * DM_TILE * (2 * D + V) * 2;
   const size_t merge = (size_t)(DM_WARPS - 1) * 32 * (8 + V) * sizeof(float);
   const size_t smem = tiles > merge ? tiles : merge;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_diff_mma_kernel<D, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_diff_mma_kernel<D, V, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attention_diff_mma_kernel<D, V, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) TS_REFUSE((int)e, "ts_attention_diff_mma: shared memory %zu: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
   const int G = H / KVH;
-  if (scratch == nullptr || counters == nullptr || G > 16) max_splits = 1;
-  dim3 grid(max(ceil_div(max_q_len * G, DM_ROWS), max_splits), KVH, B);
-  ts_launch(attention_diff_mma_kernel<D, V>, dim3(grid), dim3(DM_WARPS * 32), smem, s, out, proj, proj_stride, k_cache,
-            v_cache, block_tables, q_start, seq_lens, table_width, H, KVH, page, scale, lambda, eps, out_scale,
-            max_splits > 1 ? scratch : nullptr, counters, max_splits);
+  if (scratch == nullptr || counters == nullptr) max_splits = 1;
+  // requests whose rows fit one warp (a single token of up to 16 heads a kv head): the grid's x index is the piece of
+  // the keys; the others: it is the row tile.  Each instance leaves the other's requests alone.
+  if ((kinds & 1) && G <= 16) {
+    ts_launch(attention_diff_mma_kernel<D, V, true>, dim3(max_splits, KVH, B), dim3(DM_WARPS * 32), smem, s, out, proj,
+              proj_stride, k_cache, v_cache, block_tables, q_start, seq_lens, table_width, H, KVH, page, scale, lambda, eps,
+              out_scale, max_splits > 1 ? scratch : nullptr, counters, max_splits);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) TS_REFUSE((int)e, "ts_attention_diff_mma: %s", cudaGetErrorString(e));
+  }
+  if ((kinds & 2) && max_q_len * G > 16) {
+    ts_launch(attention_diff_mma_kernel<D, V, false>, dim3(ceil_div(max_q_len * G, DM_ROWS), KVH, B), dim3(DM_WARPS * 32), smem,
+              s, out, proj, proj_stride, k_cache, v_cache, block_tables, q_start, seq_lens, table_width, H, KVH, page, scale,
+              lambda, eps, out_scale, (float*)nullptr, counters, 1);
+  }
   TS_LAUNCH_CHECK();
 }
 
@@ -425,12 +438,13 @@ TS_API long long ts_attention_diff_mma_scratch_floats(int B, int KVH, int V, int
 
 // Arguments as ts_attention_diff; bfloat16 only; the projection rows and both caches 16-byte aligned.
 // scratch / counters (B * KVH ints, zero before the first launch; the kernel leaves them zero) / max_splits: requests
-// that bring one token have their keys cut over up to max_splits blocks; null or 1: never.
+// that bring one token have their keys cut over up to max_splits blocks; null or 1: never.  kinds: bit 0: the step
+// has requests whose rows fit one warp, bit 1: it has others (3 when the caller does not know).
 TS_API int ts_attention_diff_mma(void* out, const void* proj, int proj_stride, const void* k_cache, const void* v_cache,
                                  const int* block_tables, const int* q_start, const int* seq_lens, int B,
                                  int table_width, int max_q_len, int H, int KVH, int D, int V, int page, float scale,
                                  float lambda, float eps, float out_scale, float* scratch, int* counters,
-                                 int max_splits, void* stream) {
+                                 int max_splits, int kinds, void* stream) {
   if (B <= 0 || max_q_len <= 0) return 0;
   if (!ts_attention_diff_mma_supported(H, KVH, D, V, TS_BF16))
     TS_REFUSE(TS_ERR_UNSUPPORTED, "ts_attention_diff_mma: H=%d KVH=%d D=%d V=%d is not taken by this kernel", H, KVH, D, V);
@@ -442,7 +456,7 @@ TS_API int ts_attention_diff_mma(void* out, const void* proj, int proj_stride, c
   if (D == DD && V == VV)                                                                                            \
     return launch_diff_mma<DD, VV>((bf16*)out, (const bf16*)proj, proj_stride, (const bf16*)k_cache, (const bf16*)v_cache, \
                                    block_tables, q_start, seq_lens, B, table_width, max_q_len, H, KVH, page, scale,   \
-                                   lambda, eps, out_scale, scratch, counters, max_splits, s)
+                                   lambda, eps, out_scale, scratch, counters, max_splits, kinds, s)
   TS_DM(32, 64);
   TS_DM(32, 128);
   TS_DM(64, 64);

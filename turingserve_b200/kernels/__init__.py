@@ -115,7 +115,7 @@ class CudaOps:
             "ts_lightning": [P, P, I, P, P, P, P, I, I, I, I, I, P],
             "ts_kv_write_pair": [P, I, I, I, P, P, P, I, I, I, I, I, I, P],
             "ts_attention_diff": [P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, F, F, I, P],
-            "ts_attention_diff_mma": [P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, F, F, P, P, I, P],
+            "ts_attention_diff_mma": [P, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, F, F, P, P, I, I, P],
             "ts_router_topk": [P, P, P, P, I, I, I, I, I, I, I, P],
             "ts_moe_align": [P, I, I, P, P, P, P, P],
             "ts_grouped_linear": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
@@ -616,6 +616,11 @@ class CudaOps:
             # at most (every piece is one more partial result for the last block to fold)
             B = step.num_requests
             splits = max(1, min(self.diff_decode_splits, 2 * self.num_sms // max(1, B * KVH)))
+            # which of the kernel's two instances the step needs (the host knows every request's token count)
+            q_lens = getattr(step, "q_lens", None)
+            G = H // KVH
+            kinds = 3 if q_lens is None else ((1 if any(n * G <= 16 for n in q_lens) else 0)
+                                              | (2 if any(n * G > 16 for n in q_lens) else 0))
             scratch = counters = None
             if splits > 1:
                 scratch = self._buffer("diff_scratch", self.lib.ts_attention_diff_mma_scratch_floats(B, KVH, V, splits),
@@ -625,7 +630,7 @@ class CudaOps:
                 _ptr(out), _ptr(proj), proj.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
                 _ptr(step.q_start), _ptr(step.seq_lens), B, block_tables.shape[1], step.max_q_len, H,
                 KVH, D, V, page_size, float(scale), float(lam), float(eps), float(out_scale), _ptr(scratch),
-                _ptr(counters), splits, self._stream())
+                _ptr(counters), splits, kinds, self._stream())
             if rc != self.UNSUPPORTED:
                 self._check(rc, "attention_diff_mma")
                 return
