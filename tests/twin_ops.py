@@ -267,3 +267,168 @@ def paged_attention(out, qkv, k_cache, v_cache, block_tables, q_start, seq_lens,
         vf = torch.where(ok.any(0)[None, :, None], vf, torch.zeros_like(vf))
         o = torch.matmul(p, vf).permute(1, 0, 2).reshape(Tq, H * D)
         out[qs:qe] = o.to(out.dtype)
+
+
+# ------------------------------------------------------------------------------------------------------------
+# Twins of the kernels of the delta rule, the biased attention and the latent attention.  They are methods of
+# TwinOps (attached below) and follow the kernels' call signatures.
+
+def _delta_prepare(self, ready, proj, conv_w, a_log, dt_bias, state, step, H, G, D, V, taps, unit_eps):
+    qk, hv = G * D, H * V
+    C = 2 * qk + hv
+    tail0 = H * D * V
+    qs = step.q_start.tolist()
+    for b, slot in enumerate(step.state_slots.tolist()):
+        a, e = qs[b], qs[b + 1]
+        if e == a:
+            continue
+        tail = state[slot, tail0:tail0 + (taps - 1) * C].view(taps - 1, C)
+        x = torch.cat([tail, proj[a:e, :C].float()], 0)
+        n = e - a
+        y = torch.zeros(n, C)
+        for u in range(taps):
+            y += x[u:u + n] * conv_w[:, u]
+        y = F.silu(y)
+        q = y[:, :qk].view(n, G, D)
+        k = y[:, qk:2 * qk].view(n, G, D)
+        q = q / torch.sqrt(q.pow(2).sum(-1, keepdim=True) + unit_eps) * D ** -0.5
+        k = k / torch.sqrt(k.pow(2).sum(-1, keepdim=True) + unit_eps)
+        bb = proj[a:e, C + hv:C + hv + H].float()
+        aa = proj[a:e, C + hv + H:C + hv + 2 * H].float()
+        ready[a:e, :qk] = q.reshape(n, qk)
+        ready[a:e, qk:2 * qk] = k.reshape(n, qk)
+        ready[a:e, 2 * qk:C] = y[:, 2 * qk:]
+        ready[a:e, C:C + H] = torch.exp(-torch.exp(a_log) * F.softplus(aa + dt_bias))
+        ready[a:e, C + H:C + 2 * H] = torch.sigmoid(bb)
+        ready[a:e, C + 2 * H:] = (q * k).sum(-1)
+
+
+def _delta_scan(self, out, ready, proj, state, step, H, G, D, V, taps):
+    qk, hv = G * D, H * V
+    C = 2 * qk + hv
+    tail0 = H * D * V
+    qs = step.q_start.tolist()
+    per = H // G
+    for b, slot in enumerate(step.state_slots.tolist()):
+        a, e = qs[b], qs[b + 1]
+        if e == a:
+            continue
+        S = state[slot, :tail0].view(H, D, V)
+        for t in range(a, e):
+            q = ready[t, :qk].view(G, D).repeat_interleave(per, 0)
+            k = ready[t, qk:2 * qk].view(G, D).repeat_interleave(per, 0)
+            v = ready[t, 2 * qk:C].view(H, V)
+            g, beta = ready[t, C:C + H], ready[t, C + H:C + 2 * H]
+            S.mul_(g[:, None, None])
+            u = beta[:, None] * (v - torch.einsum("hdv,hd->hv", S, k))
+            S.add_(k[:, :, None] * u[:, None, :])
+            out[t] = torch.einsum("hdv,hd->hv", S, q).reshape(-1)
+        if taps > 1:
+            tail = state[slot, tail0:tail0 + (taps - 1) * C].view(taps - 1, C)
+            tail.copy_(torch.cat([tail, proj[a:e, :C].float()], 0)[-(taps - 1):].clone())
+
+
+def _head_gated_rmsnorm(self, out, x, gate, weight, eps, H, V):
+    T = x.shape[0]
+    o = x.float().view(T, H, V)
+    o = o / torch.sqrt(o.pow(2).mean(-1, keepdim=True) + eps) * weight.float() * F.silu(gate.float()).view(T, H, V)
+    out.copy_(o.reshape(T, H * V).to(out.dtype))
+
+
+def _rms_rows(self, out, x, col0, weight, eps):
+    n = out.shape[1]
+    r = x[:, col0:col0 + n].float()
+    out.copy_((r / torch.sqrt(r.pow(2).mean(-1, keepdim=True) + eps) * weight.float()).to(out.dtype))
+
+
+def _qk_rownorm_write(self, proj, q_w, k_w, eps, positions, coef, every, k_cache, v_cache, slots, H, G, D, page_size):
+    hd, gd = H * D, G * D
+    q, k = proj[:, :hd].float(), proj[:, hd:hd + gd].float()
+    heat = 1.0 + coef * torch.log(torch.floor((positions.float() + 1.0) / every) + 1.0)
+    qn = q / torch.sqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_w.float() * heat[:, None]
+    kn = k / torch.sqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_w.float()
+    if slots is not None:
+        m = slots >= 0
+        sl = slots[m].long()
+        k_cache[sl // page_size, :, sl % page_size, :] = kn[m].view(-1, G, D).to(k_cache.dtype)
+        v_cache[sl // page_size, :, sl % page_size, :] = proj[m, hd:hd + gd].view(-1, G, D)
+    proj[:, :hd] = qn.to(proj.dtype)
+
+
+def _pair_angles(positions, freq, magnitude):
+    a = positions.float()[:, None] * freq.float()[None, :]              # 32-bit angles, as the kernels take them
+    return torch.cos(a) * magnitude, torch.sin(a) * magnitude
+
+
+def _rotate(x, cos, sin):
+    """x [T, ..., R] float: the first 2 n dims in neighbouring pairs; cos, sin [T, n]."""
+    n = cos.shape[1]
+    shape = [x.shape[0]] + [1] * (x.dim() - 2) + [n]
+    c, s = cos.view(shape), sin.view(shape)
+    a, b = x[..., 0:2 * n:2], x[..., 1:2 * n:2]
+    out = x.clone()
+    out[..., 0:2 * n:2] = a * c - b * s
+    out[..., 1:2 * n:2] = b * c + a * s
+    return out
+
+
+def _latent_kv_write(self, proj, col0, weight, eps, positions, freq, magnitude, rot_dims, k_cache, slots, rank, R, page_size):
+    c = proj[:, col0:col0 + rank].float()
+    c = c / torch.sqrt(c.pow(2).mean(-1, keepdim=True) + eps) * weight.float()
+    cos, sin = _pair_angles(positions, freq, magnitude)
+    kr = _rotate(proj[:, col0 + rank:col0 + rank + R].float(), cos[:, :rot_dims // 2], sin[:, :rot_dims // 2])
+    m = slots >= 0
+    sl = slots[m].long()
+    k_cache[sl // page_size, 0, sl % page_size, :] = torch.cat([c, kr], -1)[m].to(k_cache.dtype)
+
+
+def _rotate_pairs(self, dst, src, positions, freq, magnitude, rot_dims):
+    cos, sin = _pair_angles(positions, freq, magnitude)
+    dst.copy_(_rotate(src.float(), cos[:, :rot_dims // 2], sin[:, :rot_dims // 2]).to(dst.dtype))
+
+
+def _batched_linear(self, out, x, w):
+    out.copy_(torch.einsum("thk,hnk->thn", x.float(), w.float()).to(out.dtype))
+
+
+def _attention_biased(self, out, q, k_cache, v_cache, block_tables, step, KVH, page_size, scale, softcap, slopes, window):
+    T, H, Dk = q.shape
+    Dv = out.shape[2]
+    G = H // KVH
+    qsl = step.q_start.tolist()
+    out.zero_()
+    for b, seq_len in enumerate(step.seq_lens.tolist()):
+        qs, qe = qsl[b], qsl[b + 1]
+        if seq_len == 0 or qe == qs:
+            continue
+        Tq = qe - qs
+        nb = -(-seq_len // page_size)
+        blocks = block_tables[b, :nb].long()
+        kk = k_cache[blocks].permute(0, 2, 1, 3).reshape(nb * page_size, KVH, Dk)[:seq_len].float()
+        if v_cache is None:
+            vv = kk[:, :, :Dv]
+        else:
+            vv = v_cache[blocks].permute(0, 2, 1, 3).reshape(nb * page_size, KVH, Dv)[:seq_len].float()
+        i = torch.arange(Tq)[:, None] + (seq_len - Tq)
+        j = torch.arange(seq_len)[None, :]
+        ok = j <= i
+        if window:
+            ok = ok & (j > i - window)
+        vv = torch.where(ok.any(0)[:, None, None], vv, torch.zeros_like(vv))      # pages a window gave back
+        kk = torch.where(ok.any(0)[:, None, None], kk, torch.zeros_like(kk))
+        for h in range(H):
+            s = (q[qs:qe, h].float() @ kk[:, h // G].t()) * scale
+            if softcap:
+                s = softcap * torch.tanh(s / softcap)
+            if slopes is not None:
+                s = s - float(slopes[h]) * (i - j).float()
+            p = torch.softmax(s.masked_fill(~ok, float("-inf")), -1)
+            out[qs:qe, h] = (p @ vv[:, h // G]).to(out.dtype)
+
+
+for _name, _fn in (("delta_prepare", _delta_prepare), ("delta_scan", _delta_scan),
+                   ("head_gated_rmsnorm", _head_gated_rmsnorm), ("rms_rows", _rms_rows),
+                   ("qk_rownorm_write", _qk_rownorm_write), ("latent_kv_write", _latent_kv_write),
+                   ("rotate_pairs", _rotate_pairs), ("batched_linear", _batched_linear),
+                   ("attention_biased", _attention_biased)):
+    setattr(TwinOps, _name, _fn)

@@ -112,6 +112,83 @@ class DiffAttentionSpec:
 
 
 @dataclass(frozen=True)
+class YarnRotarySpec:
+    """Rotary position encoding over pairs of neighbouring dimensions (2i, 2i+1) of the first ``dims``
+    dimensions of a vector, angle = position * f_i with f_i = base^(-2i/dims).  With ``factor`` set the
+    frequencies are blended (YaRN): with place(t) = dims ln(original / (2 pi t)) / (2 ln base),
+    lo = max(floor(place(fast)), 0), hi = min(ceil(place(slow)), dims - 1) and
+    ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) the frequency is f_i / factor * ramp_i + f_i (1 - ramp_i),
+    and cosine and sine are both multiplied by 0.1 ln(factor) + 1."""
+
+    base: float
+    dims: int
+    factor: float | None = None
+    original: float = 0.0
+    fast: float = 32.0
+    slow: float = 1.0
+    kind: str = "yarn_pairs"
+
+
+@dataclass(frozen=True)
+class DeltaRuleSpec:
+    """Gated delta rule: a matrix state per head, S <- g S; u = b (v - S^T k); S <- S + k u^T; o = S^T q, with
+    q, k, v = silu(short causal filter(projection)), q and k brought to unit length per head (``unit_eps``
+    inside the root) and q divided by sqrt(key_dim), b = sigmoid(projection),
+    g = exp(-exp(A) softplus(projection + dt)); query/key head floor(h / (heads / kv_heads)) serves head h;
+    each head's o is divided by its root mean square, multiplied by a weight shared by the heads and by
+    silu(gate projection); then the output projection."""
+
+    num_heads: int
+    num_kv_heads: int
+    key_dim: int
+    value_dim: int
+    conv_taps: int
+    norm_eps: float
+    unit_eps: float = 1e-6
+    kind: str = "delta_rule"
+
+
+@dataclass(frozen=True)
+class CappedAttentionSpec:
+    """Grouped-query softmax attention whose values are the key projection itself (before its norm), with
+    queries and keys RMS-normed over the whole projection row (all heads at once, learned weights), and a
+    score  cap tanh(q.k scale / cap) - slope_h (i - j)  (``softcap`` None: no cap; ``slope_power`` None: no
+    distance bias, else slope_h = 2^(-slope_power (h + 1) / heads)).  ``window`` w: position i sees
+    i - w < j <= i.  ``q_temp`` (coef, every): the query at position p is multiplied by
+    1 + coef ln(floor((p + 1) / every) + 1).  No position encoding."""
+
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    scale: float
+    norm_eps: float
+    softcap: float | None = None
+    window: int | None = None
+    q_temp: tuple[float, int] | None = None
+    slope_power: float | None = 8.0
+    kind: str = "capped_attention"
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Attention through low-rank latents: queries W_uq rms(W_dq h), per head [``nope_dim`` plain |
+    ``rope_dim`` rotated]; per token one latent c = rms(first ``kv_rank`` rows of W_dkv h) and one rotated key
+    part (the last ``rope_dim`` rows) shared by all heads; per head keys W_uk c and values W_uv c.  Causal
+    softmax of (q_plain . k_plain + q_rot . k_rot) * scale.  Only c and the rotated key part are cached."""
+
+    num_heads: int
+    nope_dim: int
+    rope_dim: int
+    value_dim: int
+    q_rank: int
+    kv_rank: int
+    scale: float
+    norm_eps: float
+    position: Any = None                # a position-encoding spec for the rotated parts
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
 class MLPSpec:
     """Dense feed-forward without a gate: down(act(up(x)))."""
 

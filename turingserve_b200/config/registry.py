@@ -121,3 +121,5 @@ def _load_builtin() -> None:
         from turingserve_b200.models import qwen2  # noqa: F401  (registers itself)
     if "Komirax" not in _ARCHITECTURES:
         from turingserve_b200.models import komirax  # noqa: F401
+    if "Pizunex" not in _ARCHITECTURES:
+        from turingserve_b200.models import pizunex  # noqa: F401

@@ -141,7 +141,8 @@ def _load_builtin() -> None:
     if not _loaded:
         _loaded = True
         from turingserve_b200.parts import (  # noqa: F401
-            attention, block, diff_attention, gated_mlp, lightning, mlp, rmsnorm, rotary, routed_mlp)
+            attention, block, capped_attention, delta_rule, diff_attention, gated_mlp, latent_attention, lightning, mlp,
+            rmsnorm, rotary, routed_mlp)
 
 
 def build_block(layer_spec: Any, ctx: BuildContext):

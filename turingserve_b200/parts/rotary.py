@@ -8,6 +8,8 @@ its arithmetic in 32-bit with one rounding (turingserve/ops/triton_rope.py:10-24
 
 from __future__ import annotations
 
+import math
+
 import torch
 
 from turingserve_b200.parts.base import BuildContext, register
@@ -28,4 +30,29 @@ class RotaryEncoding:
         self.sin = freqs.sin().to(ctx.device).contiguous()
 
 
+class PairRotaryEncoding:
+    """Rotation of neighbouring pairs (2i, 2i+1) with YaRN-blended frequencies.  No table over positions:
+    the kernels take the angle as position * ``freq[i]`` in 32-bit and multiply cosine and sine by
+    ``magnitude``, so no longest sequence has to be known.  ``freq`` is float32 [dims / 2] on the device."""
+
+    def __init__(self, spec, ctx: BuildContext) -> None:
+        self.dims = int(spec.dims)
+        if self.dims % 2 or self.dims <= 0:
+            raise ValueError("the rotated dimensions come in pairs")
+        base = float(spec.base)
+        i = torch.arange(self.dims // 2, dtype=torch.float64)
+        f = base ** (-2.0 * i / self.dims)
+        self.magnitude = 1.0
+        if spec.factor:
+            def place(t: float) -> float:
+                return self.dims * math.log(spec.original / (2.0 * math.pi * t)) / (2.0 * math.log(base))
+            lo = max(math.floor(place(spec.fast)), 0)
+            hi = min(math.ceil(place(spec.slow)), self.dims - 1)
+            ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+            f = f / float(spec.factor) * ramp + f * (1.0 - ramp)
+            self.magnitude = 0.1 * math.log(float(spec.factor)) + 1.0
+        self.freq = f.to(torch.float32).to(ctx.device).contiguous()
+
+
 register("position", "rope", RotaryEncoding)
+register("position", "yarn_pairs", PairRotaryEncoding)
