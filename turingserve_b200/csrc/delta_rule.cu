@@ -1,0 +1,343 @@
+// The gated delta rule: for every request and head a matrix state S [D, V] in 32-bit that lives in a state slot
+// between steps.  Per token, with q and k of unit length (q also divided by sqrt(D)), a decay g in (0, 1) and a
+// write strength beta in (0, 1):
+//     S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q        (o sees the token's own write).
+// q, k and v are a fused projection's columns after a causal filter of a few taps per channel and SiLU; the
+// filter's last taps - 1 inputs are kept behind S in the same slot: [H D V | (taps - 1) x C], C = 2 G D + H V.
+//
+// Three kernels:
+//   ts_delta_prepare      one block a token: filter + SiLU, unit length per head, g, beta and k.q, as 32-bit
+//                         rows [q (G D) | k (G D) | v (H V) | g (H) | beta (H) | k.q (G)]; reads the slot's filter
+//                         inputs for the tokens before the step's first, writes nothing to the slot
+//   ts_delta_scan         the recurrence, token by token for portions and single tokens alike (cutting a prompt
+//                         changes no bit); afterwards one block a request stores the filter's new last inputs
+//   ts_head_gated_rmsnorm o / rms(o) per head, times a weight shared by the heads, times silu(gate)
+//
+// The scan: one pass over the state per token.  With a = (g S)^T k and c = (g S)^T q, both sums over the old
+// state, u = beta (v - a) and o = c + (k.q) u, so the read-out needs no second pass after the write.  A column
+// of S is independent of the others: P lanes of one warp hold it (R rows each, in registers over all tokens of
+// the step), the two sums cross the P lanes by shuffles, and no block-wide barrier sits inside a token.  Tokens
+// arrive in groups of DR_GROUP rows by cp.async while the group before is computed.
+#include "common.cuh"
+#include "mma_utils.cuh"
+
+namespace {
+
+constexpr int DR_GROUP = 16;     // tokens staged at a time
+constexpr int DR_PAD = 4;        // floats between two lanes' row pieces in shared memory (bank spread)
+
+__device__ __forceinline__ void cp_async_4(void* smem, const void* gmem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+delta_prepare_kernel(float* __restrict__ ready, const T* __restrict__ proj, int proj_stride,
+                     const float* __restrict__ conv_w, const float* __restrict__ a_log,
+                     const float* __restrict__ dt_bias, const float* __restrict__ state, size_t state_stride,
+                     const int* __restrict__ token_request, const int* __restrict__ q_start,
+                     const int* __restrict__ slots, int H, int G, int D, int V, int taps, float unit_eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float f_s[];                       // [C] filtered and activated channels
+  const int t = blockIdx.x;
+  const int b = token_request[t];
+  const int t0 = q_start[b], i = t - t0;
+  const int qk = G * D, hv = H * V, C = 2 * qk + hv, W = C + 2 * H + G;
+  const float* tail = state + (size_t)slots[b] * state_stride + (size_t)H * D * V;     // [taps - 1][C]
+  float* out = ready + (size_t)t * W;
+  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+    float acc = 0.f;
+    for (int u = 0; u < taps; ++u) {
+      const int rel = i - (taps - 1) + u;              // the input's place, counted from the step's first token
+      const float x = rel >= 0 ? to_f(proj[(size_t)(t0 + rel) * proj_stride + c]) : tail[(size_t)(rel + taps - 1) * C + c];
+      acc = fmaf(conv_w[c * taps + u], x, acc);
+    }
+    const float y = acc / (1.f + expf(-acc));
+    f_s[c] = y;
+    if (c >= 2 * qk) out[c] = y;
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const float inv_sqrt_d = 1.f / sqrtf((float)D);
+  for (int g = warp; g < G; g += nwarps) {
+    const float* fq = f_s + g * D;
+    const float* fk = f_s + qk + g * D;
+    float sq = 0.f, sk = 0.f, dot = 0.f;
+    for (int d = lane; d < D; d += 32) {
+      sq = fmaf(fq[d], fq[d], sq);
+      sk = fmaf(fk[d], fk[d], sk);
+      dot = fmaf(fq[d], fk[d], dot);
+    }
+    sq = warp_sum(sq), sk = warp_sum(sk), dot = warp_sum(dot);
+    const float rq = inv_sqrt_d / sqrtf(sq + unit_eps), rk = 1.f / sqrtf(sk + unit_eps);
+    for (int d = lane; d < D; d += 32) {
+      out[g * D + d] = fq[d] * rq;
+      out[qk + g * D + d] = fk[d] * rk;
+    }
+    if (lane == 0) out[C + 2 * H + g] = dot * rq * rk;
+  }
+  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+    const T* row = proj + (size_t)t * proj_stride + C + hv;
+    const float bb = to_f(row[h]), aa = to_f(row[H + h]);
+    out[C + h] = expf(-expf(a_log[h]) * softplus_f(aa + dt_bias[h]));
+    out[C + H + h] = 1.f / (1.f + expf(-bb));
+  }
+}
+
+// R rows of a column a lane; P lanes a column; CW = 32 / P columns a warp.
+template <int R>
+__global__ void __launch_bounds__(256)
+delta_scan_kernel(float* __restrict__ out, const float* __restrict__ ready, const void* __restrict__ proj,
+                  int proj_stride, int proj_is_bf16, float* __restrict__ state, size_t state_stride,
+                  const int* __restrict__ q_start, const int* __restrict__ slots, int H, int G, int D, int V,
+                  int taps, int P, int vec4) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) float smem[];
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int t0 = q_start[b], n = q_start[b + 1] - t0;
+  if (n <= 0) return;
+  const int kvh = h / (H / G);
+  const int qk = G * D, hv = H * V, C = 2 * qk + hv, W = C + 2 * H + G;
+  const int CW = 32 / P;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int p = lane / CW, cw = lane % CW;
+  const int cols_block = nwarps * CW;
+  const int col = warp * CW + cw;                              // within the block
+  const int j = blockIdx.x * cols_block + col;
+  const bool live = j < V;
+  const int row_w = P * (R + DR_PAD);                          // floats of one token's q (or k) in shared memory
+  const int tok_w = 2 * row_w + ((cols_block + 3 + 3) & ~3);   // q | k | v of the block's columns | g, beta, k.q (16-byte rows)
+  float* base = state + (size_t)slots[b] * state_stride;
+  float* S = base + (size_t)h * D * V;
+
+  float s[R];
+#pragma unroll
+  for (int i = 0; i < R; ++i) {
+    const int d = p * R + i;
+    s[i] = (live && d < D) ? S[(size_t)d * V + j] : 0.f;
+  }
+  for (int i = threadIdx.x; i < 2 * DR_GROUP * tok_w; i += blockDim.x) smem[i] = 0.f;   // (rows beyond D stay zero)
+  __syncthreads();
+
+  auto fetch = [&](int g0, int buf) {
+    const int gn = min(DR_GROUP, n - g0);
+    float* dst0 = smem + (size_t)buf * DR_GROUP * tok_w;
+    if (vec4) {
+      const int chunks = D / 4, per_tok = 2 * chunks;
+      for (int i = threadIdx.x; i < gn * per_tok; i += blockDim.x) {
+        const int r = i / per_tok, c = i % per_tok;
+        const int which = c >= chunks, d = (which ? c - chunks : c) * 4;
+        const float* src = ready + (size_t)(t0 + g0 + r) * W + which * qk + kvh * D + d;
+        cp_async_16(dst0 + r * tok_w + which * row_w + (d / R) * (R + DR_PAD) + d % R, src, true);
+      }
+    } else {
+      for (int i = threadIdx.x; i < gn * 2 * D; i += blockDim.x) {
+        const int r = i / (2 * D), c = i % (2 * D);
+        const int which = c >= D, d = which ? c - D : c;
+        const float* src = ready + (size_t)(t0 + g0 + r) * W + which * qk + kvh * D + d;
+        cp_async_4(dst0 + r * tok_w + which * row_w + (d / R) * (R + DR_PAD) + d % R, src);
+      }
+    }
+    for (int i = threadIdx.x; i < gn * (cols_block + 3); i += blockDim.x) {
+      const int r = i / (cols_block + 3), c = i % (cols_block + 3);
+      const float* row = ready + (size_t)(t0 + g0 + r) * W;
+      float* dst = dst0 + r * tok_w + 2 * row_w + c;
+      if (c < cols_block) {
+        const int jj = blockIdx.x * cols_block + c;
+        if (jj < V) cp_async_4(dst, row + 2 * qk + h * V + jj);
+      } else if (c == cols_block) cp_async_4(dst, row + C + h);
+      else if (c == cols_block + 1) cp_async_4(dst, row + C + H + h);
+      else cp_async_4(dst, row + C + 2 * H + kvh);
+    }
+  };
+
+  fetch(0, 0);
+  cp_async_commit();
+  int buf = 0;
+  for (int g0 = 0; g0 < n; g0 += DR_GROUP, buf ^= 1) {
+    const int gn = min(DR_GROUP, n - g0);
+    if (g0 + DR_GROUP < n) fetch(g0 + DR_GROUP, buf ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();                                           // this group's rows are here
+    const float* grp = smem + (size_t)buf * DR_GROUP * tok_w;
+    for (int r = 0; r < gn; ++r) {
+      const float* tok = grp + r * tok_w;
+      const float4* qr = reinterpret_cast<const float4*>(tok + p * (R + DR_PAD));
+      const float4* kr = reinterpret_cast<const float4*>(tok + row_w + p * (R + DR_PAD));
+      float a0 = 0.f, a1 = 0.f, c0 = 0.f, c1 = 0.f;
+#pragma unroll
+      for (int i = 0; i < R / 4; ++i) {
+        const float4 k4 = kr[i], q4 = qr[i];
+        a0 = fmaf(s[4 * i + 0], k4.x, a0);
+        c0 = fmaf(s[4 * i + 0], q4.x, c0);
+        a1 = fmaf(s[4 * i + 1], k4.y, a1);
+        c1 = fmaf(s[4 * i + 1], q4.y, c1);
+        a0 = fmaf(s[4 * i + 2], k4.z, a0);
+        c0 = fmaf(s[4 * i + 2], q4.z, c0);
+        a1 = fmaf(s[4 * i + 3], k4.w, a1);
+        c1 = fmaf(s[4 * i + 3], q4.w, c1);
+      }
+      float a = a0 + a1, c = c0 + c1;
+      for (int off = CW; off < 32; off <<= 1) {
+        a += __shfl_xor_sync(0xffffffffu, a, off);
+        c += __shfl_xor_sync(0xffffffffu, c, off);
+      }
+      const float* sc = tok + 2 * row_w + cols_block;
+      const float g = sc[0], beta = sc[1], kq = sc[2];
+      const float u = beta * (tok[2 * row_w + col] - g * a);
+      const float o = fmaf(kq, u, g * c);
+#pragma unroll
+      for (int i = 0; i < R / 4; ++i) {
+        const float4 k4 = kr[i];
+        s[4 * i + 0] = fmaf(k4.x, u, g * s[4 * i + 0]);
+        s[4 * i + 1] = fmaf(k4.y, u, g * s[4 * i + 1]);
+        s[4 * i + 2] = fmaf(k4.z, u, g * s[4 * i + 2]);
+        s[4 * i + 3] = fmaf(k4.w, u, g * s[4 * i + 3]);
+      }
+      if (p == 0 && live) out[(size_t)(t0 + g0 + r) * hv + h * V + j] = o;
+    }
+    __syncthreads();                                           // the buffer may be filled again
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int i = 0; i < R; ++i) {
+    const int d = p * R + i;
+    if (live && d < D) S[(size_t)d * V + j] = s[i];
+  }
+  // the filter's new last inputs: what the slot held, moved up by n, then this step's raw rows
+  if (blockIdx.x == 0 && h == 0 && taps > 1) {
+    float* tail = base + (size_t)H * D * V;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+      float nv[8];
+#pragma unroll
+      for (int jt = 0; jt < 7; ++jt) {
+        if (jt >= taps - 1) break;
+        const int rel = n - (taps - 1) + jt;
+        if (rel >= 0) {
+          const size_t at = (size_t)(t0 + rel) * proj_stride + c;
+          nv[jt] = proj_is_bf16 ? to_f(reinterpret_cast<const bf16*>(proj)[at]) : reinterpret_cast<const float*>(proj)[at];
+        } else {
+          nv[jt] = tail[(size_t)(rel + taps - 1) * C + c];
+        }
+      }
+#pragma unroll
+      for (int jt = 0; jt < 7; ++jt) {
+        if (jt >= taps - 1) break;
+        tail[(size_t)jt * C + c] = nv[jt];
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_gated_rmsnorm_kernel(T* __restrict__ out, const float* __restrict__ x, const T* __restrict__ gate, int gate_stride,
+                          const float* __restrict__ w, float eps, int H, int V) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int h = warp; h < H; h += nwarps) {
+    const float* xr = x + ((size_t)t * H + h) * V;
+    const T* gr = gate + (size_t)t * gate_stride + (size_t)h * V;
+    float ss = 0.f;
+    for (int i = lane; i < V; i += 32) ss = fmaf(xr[i], xr[i], ss);
+    ss = warp_sum(ss);
+    const float rstd = 1.f / sqrtf(ss / (float)V + eps);
+    for (int i = lane; i < V; i += 32) {
+      const float z = to_f(gr[i]);
+      out[((size_t)t * H + h) * V + i] = from_f<T>(xr[i] * rstd * w[i] * (z / (1.f + expf(-z))));
+    }
+  }
+}
+
+}  // namespace
+
+// ready: [T, 2 G D + H V + 2 H + G] 32-bit.  proj: [T, proj_stride] rows holding q at column 0, k at G D, v at
+// 2 G D, then the gate (H V), b (H) and a (H).  conv_w: [2 G D + H V, taps] 32-bit.  state: [slots, state_stride].
+TS_API int ts_delta_prepare(float* ready, const void* proj, int proj_stride, const float* conv_w, const float* a_log,
+                            const float* dt_bias, const float* state, long long state_stride, const int* token_request,
+                            const int* q_start, const int* slots, int T, int H, int G, int D, int V, int taps,
+                            float unit_eps, int dtype, void* stream) {
+  if (T <= 0) return 0;
+  if (H <= 0 || G <= 0 || H % G || D <= 0 || V <= 0) TS_REFUSE(TS_ERR_SHAPE, "ts_delta_prepare: %d heads over %d of %d x %d", H, G, D, V);
+  if (taps < 1 || taps > 8) TS_REFUSE(TS_ERR_LIMIT, "ts_delta_prepare: %d taps (1 to 8)", taps);
+  const size_t smem = sizeof(float) * ((size_t)2 * G * D + (size_t)H * V);
+  if (smem > 200 * 1024) TS_REFUSE(TS_ERR_LIMIT, "ts_delta_prepare: %zu filtered channels", smem / 4);
+  cudaStream_t s = (cudaStream_t)stream;
+#define TS_DP(TT)                                                                                                        \
+  do {                                                                                                                   \
+    static size_t configured = 0;                                                                                        \
+    if (smem > 48 * 1024 && smem > configured) {                                                                         \
+      cudaError_t e = cudaFuncSetAttribute(delta_prepare_kernel<TT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e != cudaSuccess) TS_REFUSE((int)e, "ts_delta_prepare: shared memory %zu: %s", smem, cudaGetErrorString(e));   \
+      configured = smem;                                                                                                 \
+    }                                                                                                                    \
+    ts_launch(delta_prepare_kernel<TT>, dim3(T), dim3(128), smem, s, ready, (const TT*)proj, proj_stride, conv_w, a_log, \
+              dt_bias, state, (size_t)state_stride, token_request, q_start, slots, H, G, D, V, taps, unit_eps);          \
+  } while (0)
+  if (dtype == TS_F32) TS_DP(float);
+  else if (dtype == TS_BF16) TS_DP(bf16);
+  else TS_REFUSE(TS_ERR_DTYPE, "ts_delta_prepare: dtype %d", dtype);
+#undef TS_DP
+  TS_LAUNCH_CHECK();
+}
+
+// out: [T, H V] 32-bit.  proj: the raw projection rows (for the filter's new last inputs).
+TS_API int ts_delta_scan(float* out, const float* ready, const void* proj, int proj_stride, float* state,
+                         long long state_stride, const int* q_start, const int* slots, int B, int H, int G, int D, int V,
+                         int taps, int dtype, void* stream) {
+  if (B <= 0) return 0;
+  if (H <= 0 || G <= 0 || H % G || D <= 0 || V <= 0) TS_REFUSE(TS_ERR_SHAPE, "ts_delta_scan: %d heads over %d of %d x %d", H, G, D, V);
+  if (taps < 1 || taps > 8) TS_REFUSE(TS_ERR_LIMIT, "ts_delta_scan: %d taps (1 to 8)", taps);
+  if (dtype != TS_F32 && dtype != TS_BF16) TS_REFUSE(TS_ERR_DTYPE, "ts_delta_scan: dtype %d", dtype);
+  if (B > 65535 || H > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_delta_scan: %d requests / %d heads per launch", B, H);
+  const int R = D > 64 ? 32 : 16;
+  int P = 1;
+  while (P * R < D) P <<= 1;
+  if (P > 32) TS_REFUSE(TS_ERR_LIMIT, "ts_delta_scan: keys of %d (limit 1024)", D);
+  const int CW = 32 / P;
+  const int nwarps = min(8, ceil_div(V, CW));
+  const int cols_block = nwarps * CW;
+  const int W = 2 * G * D + H * V + 2 * H + G;
+  const int vec4 = D % 4 == 0 && W % 4 == 0 && (G * D) % 4 == 0 && !((uintptr_t)ready & 15);
+  const size_t smem = sizeof(float) * 2 * DR_GROUP * ((size_t)2 * P * (R + DR_PAD) + ((cols_block + 3 + 3) & ~3));
+  if (smem > 200 * 1024) TS_REFUSE(TS_ERR_LIMIT, "ts_delta_scan: shared memory %zu", smem);
+  cudaStream_t s = (cudaStream_t)stream;
+  dim3 grid(ceil_div(V, cols_block), H, B);
+#define TS_DS(RR)                                                                                                        \
+  do {                                                                                                                   \
+    static size_t configured = 0;                                                                                        \
+    if (smem > 48 * 1024 && smem > configured) {                                                                         \
+      cudaError_t e = cudaFuncSetAttribute(delta_scan_kernel<RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e != cudaSuccess) TS_REFUSE((int)e, "ts_delta_scan: shared memory %zu: %s", smem, cudaGetErrorString(e));      \
+      configured = smem;                                                                                                 \
+    }                                                                                                                    \
+    ts_launch(delta_scan_kernel<RR>, dim3(grid), dim3(nwarps * 32), smem, s, out, ready, proj, proj_stride,              \
+              dtype == TS_BF16 ? 1 : 0, state, (size_t)state_stride, q_start, slots, H, G, D, V, taps, P, vec4);         \
+  } while (0)
+  if (R == 32) TS_DS(32);
+  else TS_DS(16);
+#undef TS_DS
+  TS_LAUNCH_CHECK();
+}
+
+// out [T, H V] = x / sqrt(mean over a head's V of x^2 + eps) * w[V] * silu(gate); x 32-bit [T, H V]; gate rows
+// gate_stride apart.
+TS_API int ts_head_gated_rmsnorm(void* out, const float* x, const void* gate, int gate_stride, const float* w, float eps,
+                                 int T, int H, int V, int dtype, void* stream) {
+  if (T <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == TS_F32)
+    ts_launch(head_gated_rmsnorm_kernel<float>, dim3(T), dim3(128), 0, s, (float*)out, x, (const float*)gate, gate_stride, w, eps, H, V);
+  else if (dtype == TS_BF16)
+    ts_launch(head_gated_rmsnorm_kernel<bf16>, dim3(T), dim3(128), 0, s, (bf16*)out, x, (const bf16*)gate, gate_stride, w, eps, H, V);
+  else
+    TS_REFUSE(TS_ERR_DTYPE, "ts_head_gated_rmsnorm: dtype %d", dtype);
+  TS_LAUNCH_CHECK();
+}

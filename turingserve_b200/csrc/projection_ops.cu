@@ -1,0 +1,264 @@
+// What sits between a projection and the attention that consumes it, for mixers that norm, rotate or re-project
+// their queries and keys; 32-bit arithmetic and one rounding everywhere:
+//   ts_rms_rows          out = x[:, col0 : col0 + n] / rms * w               (a column slice of wider rows)
+//   ts_qk_rownorm_write  q and k normed over their WHOLE rows (all heads at once), q times a temperature that grows
+//                        with the position; normed keys into the key cache, the keys as projected into the value cache
+//   ts_latent_kv_write   one cached row a token: [rms(latent) * w | rotated key part]
+//   ts_rotate_pairs      rotation of neighbouring pairs (2i, 2i+1), angle = position * freq[i] in 32-bit, cosine and
+//                        sine times a magnitude; strided source and destination
+//   ts_batched_linear    out[t, h, :] = w[h] x[t, h, :], a product per head over strided rows (FFMA, fixed k order)
+#include "common.cuh"
+
+namespace {
+
+template <typename T>
+__global__ void rms_rows_kernel(T* __restrict__ out, const T* __restrict__ x, int x_stride, int col0, int n,
+                                const float* __restrict__ w, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[32];
+  const T* xr = x + (size_t)blockIdx.x * x_stride + col0;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = to_f(xr[i]);
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float rstd = 1.f / sqrtf(ss / (float)n + eps);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) out[(size_t)blockIdx.x * n + i] = from_f<T>(to_f(xr[i]) * rstd * w[i]);
+}
+
+template <typename T>
+__global__ void qk_rownorm_write_kernel(T* __restrict__ proj, int stride, const float* __restrict__ q_w,
+                                        const float* __restrict__ k_w, float eps, const int* __restrict__ positions,
+                                        float coef, int every, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                        const int* __restrict__ slots, int H, int G, int D, int page) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  T* row = proj + (size_t)t * stride;
+  const int hd = H * D, gd = G * D;
+  float sq = 0.f, sk = 0.f;
+  for (int i = threadIdx.x; i < hd; i += blockDim.x) {
+    const float v = to_f(row[i]);
+    sq = fmaf(v, v, sq);
+  }
+  for (int i = threadIdx.x; i < gd; i += blockDim.x) {
+    const float v = to_f(row[hd + i]);
+    sk = fmaf(v, v, sk);
+  }
+  sq = block_sum(sq, scratch);
+  sk = block_sum(sk, scratch);
+  const int p = positions[t];
+  // (p + 1) / every as an integer division: the floor of the quotient of two positive integers
+  const float heat = coef != 0.f ? 1.f + coef * logf((float)((p + 1) / every) + 1.f) : 1.f;
+  const float rq = heat / sqrtf(sq / (float)hd + eps), rk = 1.f / sqrtf(sk / (float)gd + eps);
+  const int slot = slots != nullptr ? slots[t] : -1;
+  if (slot >= 0) {
+    const size_t pg = slot / page, off = slot % page;
+    for (int i = threadIdx.x; i < gd; i += blockDim.x) {
+      const int g = i / D, d = i % D;
+      const size_t at = ((pg * G + g) * page + off) * D + d;
+      const T raw = row[hd + i];
+      k_cache[at] = from_f<T>(to_f(raw) * rk * k_w[i]);
+      v_cache[at] = raw;
+    }
+  }
+  for (int i = threadIdx.x; i < hd; i += blockDim.x) row[i] = from_f<T>(to_f(row[i]) * rq * q_w[i]);
+}
+
+__device__ __forceinline__ void pair_angle(int pos, float f, float magnitude, float& c, float& s) {
+  const float a = (float)pos * f;
+  sincosf(a, &s, &c);
+  c *= magnitude;
+  s *= magnitude;
+}
+
+template <typename T>
+__global__ void latent_kv_write_kernel(const T* __restrict__ proj, int stride, int col0, const float* __restrict__ w,
+                                       float eps, const int* __restrict__ positions, const float* __restrict__ freq,
+                                       float magnitude, int rot_dims, T* __restrict__ k_cache,
+                                       const int* __restrict__ slots, int rank, int R, int page) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[32];
+  const int t = blockIdx.x;
+  const int slot = slots[t];
+  if (slot < 0) return;
+  const T* row = proj + (size_t)t * stride + col0;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) {
+    const float v = to_f(row[i]);
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float rstd = 1.f / sqrtf(ss / (float)rank + eps);
+  T* dst = k_cache + ((size_t)(slot / page) * page + slot % page) * (rank + R);        // one kv head
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) dst[i] = from_f<T>(to_f(row[i]) * rstd * w[i]);
+  const int pos = positions[t];
+  for (int i = threadIdx.x; i < R / 2 + (R & 1); i += blockDim.x) {
+    const int d = 2 * i;
+    if (d < rot_dims) {                                  // (rot_dims is even and at most R)
+      float c, s;
+      pair_angle(pos, freq[i], magnitude, c, s);
+      const float u = to_f(row[rank + d]), v = to_f(row[rank + d + 1]);
+      dst[rank + d] = from_f<T>(u * c - v * s);
+      dst[rank + d + 1] = from_f<T>(v * c + u * s);
+    } else {
+      dst[rank + d] = row[rank + d];
+      if (d + 1 < R) dst[rank + d + 1] = row[rank + d + 1];
+    }
+  }
+}
+
+template <typename T>
+__global__ void rotate_pairs_kernel(T* __restrict__ dst, int dst_ts, int dst_hs, const T* __restrict__ src, int src_ts,
+                                    int src_hs, const int* __restrict__ positions, const float* __restrict__ freq,
+                                    float magnitude, int rot_dims, int H, int R) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int half = R / 2 + (R & 1);
+  for (int idx = threadIdx.x; idx < H * half; idx += blockDim.x) {
+    const int h = idx / half, i = idx % half, d = 2 * i;
+    const T* a = src + (size_t)t * src_ts + (size_t)h * src_hs;
+    T* o = dst + (size_t)t * dst_ts + (size_t)h * dst_hs;
+    if (d < rot_dims) {                                  // (rot_dims is even and at most R)
+      float c, s;
+      pair_angle(pos, freq[i], magnitude, c, s);
+      const float u = to_f(a[d]), v = to_f(a[d + 1]);
+      o[d] = from_f<T>(u * c - v * s);
+      o[d + 1] = from_f<T>(v * c + u * s);
+    } else {
+      o[d] = a[d];
+      if (d + 1 < R) o[d + 1] = a[d + 1];
+    }
+  }
+}
+
+constexpr int BL_M = 64, BL_N = 64, BL_K = 16, BL_PAD = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+batched_linear_kernel(T* __restrict__ out, int out_ts, int out_hs, const T* __restrict__ x, int x_ts, int x_hs,
+                      const T* __restrict__ w, int M, int N, int K) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ __align__(16) float As[BL_K][BL_M + BL_PAD];
+  __shared__ __align__(16) float Ws[BL_K][BL_N + BL_PAD];
+  const int tid = threadIdx.x;
+  const int h = blockIdx.z;
+  const int m0 = blockIdx.y * BL_M, n0 = blockIdx.x * BL_N;
+  const int lr = tid >> 2, lk = (tid & 3) * 4;
+  const int ty = tid >> 4, tx = tid & 15;
+  float acc[4][4] = {};
+  const int am = m0 + lr;
+  const T* a_row = am < M ? x + (size_t)am * x_ts + (size_t)h * x_hs : nullptr;
+  const int wn = n0 + lr;
+  const T* w_row = wn < N ? w + ((size_t)h * N + wn) * K : nullptr;
+  for (int k0 = 0; k0 < K; k0 += BL_K) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int k = k0 + lk + i;
+      As[lk + i][lr] = (a_row != nullptr && k < K) ? to_f(a_row[k]) : 0.f;
+      Ws[lk + i][lr] = (w_row != nullptr && k < K) ? to_f(w_row[k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < BL_K; ++k) {
+      const float4 a = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
+      const float4 b = *reinterpret_cast<const float4*>(&Ws[k][tx * 4]);
+      const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < N) out[(size_t)m * out_ts + (size_t)h * out_hs + n] = from_f<T>(acc[i][j]);
+    }
+  }
+}
+
+int threads_for_row(int n) { return n >= 2048 ? 512 : (n >= 512 ? 256 : 128); }
+
+}  // namespace
+
+#define TS_BY_TYPE(name, CALL)                                   \
+  do {                                                           \
+    if (dtype == TS_F32) { using TT = float; CALL; }             \
+    else if (dtype == TS_BF16) { using TT = bf16; CALL; }        \
+    else TS_REFUSE(TS_ERR_DTYPE, name ": dtype %d", dtype);      \
+  } while (0)
+
+TS_API int ts_rms_rows(void* out, const void* x, int x_stride, int col0, int n, const float* w, float eps, int T, int dtype,
+                       void* stream) {
+  if (T <= 0 || n <= 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  TS_BY_TYPE("ts_rms_rows", ts_launch(rms_rows_kernel<TT>, dim3(T), dim3(threads_for_row(n)), 0, s, (TT*)out, (const TT*)x,
+                                      x_stride, col0, n, w, eps));
+  TS_LAUNCH_CHECK();
+}
+
+// proj [T, stride]: q in columns [0, H D), k in [H D, (H + G) D).  slots null: nothing is cached.
+TS_API int ts_qk_rownorm_write(void* proj, int stride, const float* q_w, const float* k_w, float eps, const int* positions,
+                               float coef, int every, void* k_cache, void* v_cache, const int* slots, int T, int H, int G,
+                               int D, int page, int dtype, void* stream) {
+  if (T <= 0) return 0;
+  if (every < 1) TS_REFUSE(TS_ERR_SHAPE, "ts_qk_rownorm_write: every = %d", every);
+  cudaStream_t s = (cudaStream_t)stream;
+  TS_BY_TYPE("ts_qk_rownorm_write",
+             ts_launch(qk_rownorm_write_kernel<TT>, dim3(T), dim3(threads_for_row(H * D)), 0, s, (TT*)proj, stride, q_w, k_w,
+                       eps, positions, coef, every, (TT*)k_cache, (TT*)v_cache, slots, H, G, D, page));
+  TS_LAUNCH_CHECK();
+}
+
+// proj [T, stride]: the latent in columns [col0, col0 + rank), the key part to rotate in the R columns behind it.
+// k_cache [pages, 1, page, rank + R].
+TS_API int ts_latent_kv_write(const void* proj, int stride, int col0, const float* w, float eps, const int* positions,
+                              const float* freq, float magnitude, int rot_dims, void* k_cache, const int* slots, int T,
+                              int rank, int R, int page, int dtype, void* stream) {
+  if (T <= 0) return 0;
+  if (rot_dims % 2 || rot_dims > R) TS_REFUSE(TS_ERR_SHAPE, "ts_latent_kv_write: %d rotated dimensions of %d", rot_dims, R);
+  cudaStream_t s = (cudaStream_t)stream;
+  TS_BY_TYPE("ts_latent_kv_write",
+             ts_launch(latent_kv_write_kernel<TT>, dim3(T), dim3(threads_for_row(rank)), 0, s, (const TT*)proj, stride, col0, w,
+                       eps, positions, freq, magnitude, rot_dims, (TT*)k_cache, slots, rank, R, page));
+  TS_LAUNCH_CHECK();
+}
+
+// dst[t, h, :R] = rotate(src[t, h, :R]); strides in elements.
+TS_API int ts_rotate_pairs(void* dst, int dst_ts, int dst_hs, const void* src, int src_ts, int src_hs, const int* positions,
+                           const float* freq, float magnitude, int rot_dims, int T, int H, int R, int dtype, void* stream) {
+  if (T <= 0 || H <= 0 || R <= 0) return 0;
+  if (rot_dims % 2 || rot_dims > R) TS_REFUSE(TS_ERR_SHAPE, "ts_rotate_pairs: %d rotated dimensions of %d", rot_dims, R);
+  cudaStream_t s = (cudaStream_t)stream;
+  TS_BY_TYPE("ts_rotate_pairs",
+             ts_launch(rotate_pairs_kernel<TT>, dim3(T), dim3(threads_for_row(H * R / 2)), 0, s, (TT*)dst, dst_ts, dst_hs,
+                       (const TT*)src, src_ts, src_hs, positions, freq, magnitude, rot_dims, H, R));
+  TS_LAUNCH_CHECK();
+}
+
+// out[t, h, :N] = w[h] (N x K) . x[t, h, :K]; w [H, N, K] contiguous; strides in elements.
+TS_API int ts_batched_linear(void* out, int out_ts, int out_hs, const void* x, int x_ts, int x_hs, const void* w, int T, int H,
+                             int N, int K, int dtype, void* stream) {
+  if (T <= 0 || H <= 0 || N <= 0) return 0;
+  if (K <= 0) TS_REFUSE(TS_ERR_SHAPE, "ts_batched_linear: K = %d", K);
+  dim3 grid(ceil_div(N, BL_N), ceil_div(T, BL_M), H);
+  if (grid.y > 65535 || H > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_batched_linear: %d rows / %d heads per launch", T, H);
+  cudaStream_t s = (cudaStream_t)stream;
+  TS_BY_TYPE("ts_batched_linear",
+             ts_launch(batched_linear_kernel<TT>, dim3(grid), dim3(256), 0, s, (TT*)out, out_ts, out_hs, (const TT*)x, x_ts, x_hs,
+                       (const TT*)w, T, N, K));
+  TS_LAUNCH_CHECK();
+}

@@ -68,7 +68,7 @@ class LazyProduct:
 class CudaOps:
     """ctypes front of ``libturingserve_b200.so``."""
 
-    ABI = 9
+    ABI = 10
     UNSUPPORTED = -4            # a kernel's refusal of a shape or layout another kernel takes
 
     def __init__(self, lib_path: str) -> None:
@@ -121,6 +121,15 @@ class CudaOps:
             "ts_grouped_linear": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
             "ts_moe_combine": [P, P, P, P, I, I, I, I, P],
             "ts_moe_gather": [P, P, P, P, I, I, I, I, P],
+            "ts_delta_prepare": [P, P, I, P, P, P, P, ctypes.c_longlong, P, P, P, I, I, I, I, I, I, F, I, P],
+            "ts_delta_scan": [P, P, P, I, P, ctypes.c_longlong, P, P, I, I, I, I, I, I, I, P],
+            "ts_head_gated_rmsnorm": [P, P, P, I, P, F, I, I, I, I, P],
+            "ts_attention_biased": [P, I, I, P, I, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, P, I, I, P, P, I, P],
+            "ts_rms_rows": [P, P, I, I, I, P, F, I, I, P],
+            "ts_qk_rownorm_write": [P, I, P, P, F, P, F, I, P, P, P, I, I, I, I, I, I, P],
+            "ts_latent_kv_write": [P, I, I, P, F, P, P, F, I, P, P, I, I, I, I, I, P],
+            "ts_rotate_pairs": [P, I, I, P, I, I, P, P, F, I, I, I, I, I, P],
+            "ts_batched_linear": [P, I, I, P, I, I, P, I, I, I, I, I, P],
         }
         for name, args in sigs.items():
             fn = getattr(self.lib, name)
@@ -130,6 +139,8 @@ class CudaOps:
         self.lib.ts_attention_diff_mma_supported.restype = c_int
         self.lib.ts_attention_diff_mma_scratch_floats.argtypes = [I, I, I, I]
         self.lib.ts_attention_diff_mma_scratch_floats.restype = ctypes.c_longlong
+        self.lib.ts_attention_biased_scratch_floats.argtypes = [I, I, I, I, I, I]
+        self.lib.ts_attention_biased_scratch_floats.restype = ctypes.c_longlong
         self.lib.ts_rmsnorm_wide_takes_parts.argtypes = [I]
         self.lib.ts_rmsnorm_wide_takes_parts.restype = c_int
         self.lib.ts_moe_tile_rows.argtypes = []
@@ -638,6 +649,121 @@ class CudaOps:
             _ptr(out), _ptr(proj), proj.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables), _ptr(step.q_start),
             _ptr(step.seq_lens), step.num_requests, block_tables.shape[1], step.max_q_len, H, KVH, D, V, page_size,
             float(scale), float(lam), float(eps), float(out_scale), _code(proj.dtype), self._stream()), "attention_diff")
+
+    # -- the gated delta rule --------------------------------------------------------------------------------------
+    def delta_prepare(self, ready, proj, conv_w, a_log, dt_bias, state, step, H: int, G: int, D: int, V: int, taps: int,
+                      unit_eps: float) -> None:
+        """ready (float32 [T, 2GD + HV + 2H + G]) = [q | k | v | g | beta | k.q] of every token: the columns q, k, v of
+        ``proj`` through their causal filters (``conv_w`` float32 [2GD + HV, taps]; inputs before the step's first
+        token come from the request's state slot) and SiLU, q and k to unit length per head and q / sqrt(D),
+        g = exp(-exp(a_log) softplus(a + dt_bias)), beta = sigmoid(b); b and a are the last 2H columns of ``proj``."""
+        T = proj.shape[0]
+        self._check(self.lib.ts_delta_prepare(_ptr(ready), _ptr(proj), proj.stride(0), _ptr(conv_w), _ptr(a_log),
+                                              _ptr(dt_bias), _ptr(state), state.stride(0), _ptr(step.token_request),
+                                              _ptr(step.q_start), _ptr(step.state_slots), T, H, G, D, V, taps,
+                                              float(unit_eps), _code(proj.dtype), self._stream()), "delta_prepare")
+
+    def delta_scan(self, out, ready, proj, state, step, H: int, G: int, D: int, V: int, taps: int) -> None:
+        """out (float32 [T, HV]): the recurrence over the rows ``delta_prepare`` made; ``state`` (float32
+        [slots, HDV + (taps - 1)(2GD + HV)]) is read and left updated at each request's slot, the filter's last
+        inputs (from ``proj``) included."""
+        self._check(self.lib.ts_delta_scan(_ptr(out), _ptr(ready), _ptr(proj), proj.stride(0), _ptr(state), state.stride(0),
+                                           _ptr(step.q_start), _ptr(step.state_slots), step.num_requests, H, G, D, V, taps,
+                                           _code(proj.dtype), self._stream()), "delta_scan")
+
+    def head_gated_rmsnorm(self, out, x, gate, weight, eps: float, H: int, V: int) -> None:
+        """out [T, HV] = x / rms over each head's V * weight[V] * silu(gate); x float32; ``gate`` possibly a column
+        slice of a wider tensor."""
+        if gate.stride(1) != 1:
+            raise ValueError("head_gated_rmsnorm: the gate's rows must be contiguous")
+        self._check(self.lib.ts_head_gated_rmsnorm(_ptr(out), _ptr(x), _ptr(gate), gate.stride(0), _ptr(weight), float(eps),
+                                                   x.shape[0], H, V, _code(out.dtype), self._stream()), "head_gated_rmsnorm")
+
+    # -- norms, rotations and per-head products around an attention ----------------------------------------------------
+    def rms_rows(self, out, x, col0: int, weight, eps: float) -> None:
+        """out [T, n] = rms norm of the columns col0 .. col0 + n of ``x`` times ``weight`` (float32)."""
+        T, n = out.shape
+        self._check(self.lib.ts_rms_rows(_ptr(out), _ptr(x), x.stride(0), col0, n, _ptr(weight), float(eps), T,
+                                         _code(x.dtype), self._stream()), "rms_rows")
+
+    def qk_rownorm_write(self, proj, q_w, k_w, eps: float, positions, coef: float, every: int, k_cache, v_cache, slots,
+                         H: int, G: int, D: int, page_size: int) -> None:
+        """``proj`` [T, (H + G) D] = [q | k]: q normed over its whole row, times ``q_w`` and the temperature
+        1 + coef ln(floor((p + 1) / every) + 1), in place; k normed over its whole row times ``k_w`` into ``k_cache``
+        and k as projected into ``v_cache`` at ``slots`` (None: nothing is cached)."""
+        self._check(self.lib.ts_qk_rownorm_write(_ptr(proj), proj.stride(0), _ptr(q_w), _ptr(k_w), float(eps), _ptr(positions),
+                                                 float(coef), int(every), _ptr(k_cache), _ptr(v_cache), _ptr(slots),
+                                                 proj.shape[0], H, G, D, page_size, _code(proj.dtype), self._stream()),
+                    "qk_rownorm_write")
+
+    def latent_kv_write(self, proj, col0: int, weight, eps: float, positions, freq, magnitude: float, rot_dims: int, k_cache,
+                        slots, rank: int, R: int, page_size: int) -> None:
+        """The cached row of every token, [rms(latent) * weight | rotated key part], from the columns col0 .. of
+        ``proj`` into ``k_cache`` [pages, 1, page, rank + R] at ``slots``."""
+        self._check(self.lib.ts_latent_kv_write(_ptr(proj), proj.stride(0), col0, _ptr(weight), float(eps), _ptr(positions),
+                                                _ptr(freq), float(magnitude), rot_dims, _ptr(k_cache), _ptr(slots),
+                                                proj.shape[0], rank, R, page_size, _code(proj.dtype), self._stream()),
+                    "latent_kv_write")
+
+    def rotate_pairs(self, dst, src, positions, freq, magnitude: float, rot_dims: int) -> None:
+        """dst[t, h, :] = src[t, h, :] with its first ``rot_dims`` dimensions rotated in neighbouring pairs by
+        position * freq[i] (cosine and sine times ``magnitude``); [T, H, R] views with unit last stride."""
+        T, H, R = src.shape
+        if dst.stride(2) != 1 or src.stride(2) != 1:
+            raise ValueError("rotate_pairs: rows must be contiguous")
+        self._check(self.lib.ts_rotate_pairs(_ptr(dst), dst.stride(0), dst.stride(1), _ptr(src), src.stride(0), src.stride(1),
+                                             _ptr(positions), _ptr(freq), float(magnitude), rot_dims, T, H, R,
+                                             _code(src.dtype), self._stream()), "rotate_pairs")
+
+    # bfloat16 per-head products with at least this many rows go to the library's batched product
+    batched_library_rows = int(os.environ.get("TURINGSERVE_B200_BATCHED_LIBRARY_ROWS", "64"))
+
+    def batched_linear(self, out, x, w) -> None:
+        """out[t, h, :] = w[h] x[t, h, :]: ``x`` [T, H, K] and ``out`` [T, H, N] views with unit last stride,
+        ``w`` [H, N, K] contiguous.  float32: this library's FFMA kernel (fixed k order); bfloat16 with many rows:
+        the vendor's batched product."""
+        T, H, K = x.shape
+        N = w.shape[1]
+        if out.stride(2) != 1 or x.stride(2) != 1 or not w.is_contiguous():
+            raise ValueError("batched_linear: rows must be contiguous")
+        if x.dtype == torch.bfloat16 and self.use_library_gemm and T >= self.batched_library_rows:
+            torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1))
+            return
+        self._check(self.lib.ts_batched_linear(_ptr(out), out.stride(0), out.stride(1), _ptr(x), x.stride(0), x.stride(1),
+                                               _ptr(w), T, H, N, K, _code(x.dtype), self._stream()), "batched_linear")
+
+    biased_decode_splits = int(os.environ.get("TURINGSERVE_B200_BIASED_DECODE_SPLITS", "0"))
+
+    def attention_biased(self, out, q, k_cache, v_cache, block_tables, step, KVH: int, page_size: int, scale: float,
+                         softcap: float, slopes, window) -> None:
+        """out [T, H, Dv] = softmax over the visible keys of cap tanh(q.k scale / cap) - slope_h (i - j), times the
+        values; q [T, H, Dk] (views with unit last stride).  ``v_cache`` None: the values are the first Dv columns
+        of the key rows.  ``softcap`` 0: none; ``slopes`` (float32 [H]) None: none; ``window`` None: none.  The keys
+        of requests that bring one token are cut over several blocks when the step's longest context is long."""
+        T, H, Dk = q.shape
+        Dv = out.shape[2]
+        if out.stride(2) != 1 or q.stride(2) != 1:
+            raise ValueError("attention_biased: rows must be contiguous")
+        B = step.num_requests
+        w = 0 if window is None else int(window)
+        reach = min(step.max_seq_len, w) if w else step.max_seq_len
+        splits = self.biased_decode_splits
+        if splits <= 0:
+            # single-token requests: so many pieces that the chip has two blocks an SM, each with four tiles or more
+            splits = 1
+            if step.num_decode > 0:
+                splits = max(1, min(32, 2 * self.num_sms // max(1, step.num_decode * KVH), reach // 128))
+        scratch = counters = None
+        if splits > 1:
+            scratch = self._buffer("biased_scratch", self.lib.ts_attention_biased_scratch_floats(B, KVH, H, step.max_q_len, Dv, splits),
+                                   torch.float32, q.device, floor=1 << 20)
+            tiles = -(-(step.max_q_len * (H // KVH)) // 16)
+            counters = self._buffer("biased_counters", B * KVH * tiles, torch.int32, q.device, floor=1 << 14, zero=True)
+        self._check(self.lib.ts_attention_biased(
+            _ptr(out), out.stride(0), out.stride(1), _ptr(q), q.stride(0), q.stride(1), _ptr(k_cache), _ptr(v_cache),
+            _ptr(block_tables), _ptr(step.q_start), _ptr(step.seq_lens), B, block_tables.shape[1], step.max_q_len, H, KVH,
+            Dk, Dv, page_size, float(scale), float(softcap), _ptr(slopes), w, splits, _ptr(scratch), _ptr(counters),
+            _code(q.dtype), self._stream()), "attention_biased")
 
     # -- routed feed-forward ---------------------------------------------------------------------------------
     def router_topk(self, idx, weights, x, w_router, softmax: bool, renormalize: bool) -> None:
