@@ -278,11 +278,13 @@ def plain_attention(q, k, v, KVH, scale, cap, slopes, window, first_pos):
 @pytest.mark.parametrize("H,KVH,Dk,Dv,page,window,cap,shared", [
     (4, 2, 16, 16, 8, 9, 6.0, False), (6, 6, 8, 8, 4, 33, None, False), (2, 1, 40, 40, 16, 3, 20.0, False),
     (4, 1, 28, 20, 16, None, None, True), (3, 1, 80, 64, 64, None, None, True), (4, 2, 64, 64, 64, 70, 30.0, False),
-    (20, 1, 30, 30, 8, None, 4.0, False)])
+    (20, 1, 30, 30, 8, None, 4.0, False), (6, 2, 128, 128, 16, 40, 50.0, False), (5, 1, 576, 512, 64, None, None, True),
+    (3, 1, 320, 256, 16, None, None, True), (4, 4, 64, 64, 8, None, None, False)])
 def test_biased_attention_in_batches_of_unequal_requests(ops, dtype, H, KVH, Dk, Dv, page, window, cap, shared):
     """A prompt from position 0, a portion in the middle of a context, two single tokens (one with a context of one
     key), in one launch, pages in a shuffled pool; against each request alone in the plain functions.  ``shared``:
-    no value tensor, the values are the first Dv columns of the key rows."""
+    no value tensor, the values are the first Dv columns of the key rows.  In bfloat16 the widths 64, 128, 320 and 576
+    go to the tensor-core kernel (values in chunks of 128 columns, keys of single tokens cut over blocks)."""
     g = torch.Generator(device=DEV).manual_seed(H * Dk)
     q_lens, seq_lens = [1, 1, 21, 13], [1, 77, 21, 90]
     slopes = plain.slopes(H).to(DEV) if not shared else None
@@ -321,12 +323,13 @@ def test_biased_attention_in_batches_of_unequal_requests(ops, dtype, H, KVH, Dk,
 
 @pytest.mark.parametrize("decode", [False, True])
 @pytest.mark.parametrize("window,page", [(40, 16), (64, 64), (5, 8), (None, 16)])
-def test_one_loud_key_far_away_at_page_edges_and_at_the_windows_edge(ops, window, page, decode):
-    """float32, built inputs: all keys are silent but one, whose value is marked.  The query finds it hundreds of
+@pytest.mark.parametrize("dtype,D", [(torch.float32, 12), (torch.bfloat16, 64), (torch.bfloat16, 128)])
+def test_one_loud_key_far_away_at_page_edges_and_at_the_windows_edge(ops, window, page, decode, dtype, D):
+    """Built inputs (float32 on the any-size kernel, bfloat16 on the tensor cores): all keys are silent but one, whose value is marked.  The query finds it hundreds of
     tokens back (no window), at a page's last and first place, at the last place the window still holds; and it
     must not find it one place further back, nor one place ahead of itself.  ``decode``: the query comes alone
     (keys cut over several blocks) or at the end of a portion of 30."""
-    H, KVH, D = 2, 1, 12
+    H, KVH = 2, 1
     T = 700
     n_q = 1 if decode else 30
     i = T - 1
@@ -336,17 +339,17 @@ def test_one_loud_key_far_away_at_page_edges_and_at_the_windows_edge(ops, window
     else:
         cases += [i - 500, 3 * page - 1, 3 * page]
     for j in cases:
-        k = torch.zeros(T + 1, KVH, D, device=DEV)
-        v = torch.zeros(T + 1, KVH, D, device=DEV)
+        k = torch.zeros(T + 1, KVH, D, dtype=dtype, device=DEV)
+        v = torch.zeros(T + 1, KVH, D, dtype=dtype, device=DEV)
         k[j, 0, 3] = 60.0
         v[j, 0, 7] = 1.0
         k[T, 0, 3] = 90.0                                      # one place ahead of the query: in the cache's page, unseen
         v[T, 0, 5] = 1.0
         k_cache, order = paged(k, page, order=list(range(-(-(T + 1) // page), 0, -1)))
         v_cache, _ = paged(v, page, order=order)
-        q = torch.zeros(n_q, H, D, device=DEV)
+        q = torch.zeros(n_q, H, D, dtype=dtype, device=DEV)
         q[:, :, 3] = 1.0
-        out = torch.empty(n_q, H, D, device=DEV)
+        out = torch.empty(n_q, H, D, dtype=dtype, device=DEV)
         step = attention_step([n_q], [T])
         ops.attention_biased(out, q, k_cache, v_cache, i32([order]), step, KVH, page, 1.0, 0.0, None, window)
         seen = window is None or i - j < window

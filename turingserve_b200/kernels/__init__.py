@@ -125,6 +125,7 @@ class CudaOps:
             "ts_delta_scan": [P, P, P, I, P, ctypes.c_longlong, P, P, I, I, I, I, I, I, I, P],
             "ts_head_gated_rmsnorm": [P, P, P, I, P, F, I, I, I, I, P],
             "ts_attention_biased": [P, I, I, P, I, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, P, I, I, P, P, I, P],
+            "ts_attention_biased_mma": [P, I, I, P, I, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, P, I, I, P, P, P],
             "ts_rms_rows": [P, P, I, I, I, P, F, I, I, P],
             "ts_qk_rownorm_write": [P, I, P, P, F, P, F, I, P, P, P, I, I, I, I, I, I, P],
             "ts_latent_kv_write": [P, I, I, P, F, P, P, F, I, P, P, I, I, I, I, I, P],
@@ -139,6 +140,12 @@ class CudaOps:
         self.lib.ts_attention_diff_mma_supported.restype = c_int
         self.lib.ts_attention_diff_mma_scratch_floats.argtypes = [I, I, I, I]
         self.lib.ts_attention_diff_mma_scratch_floats.restype = ctypes.c_longlong
+        self.lib.ts_attention_biased_mma_supported.argtypes = [I, I, I, I, I, I]
+        self.lib.ts_attention_biased_mma_supported.restype = c_int
+        self.lib.ts_attention_biased_mma_chunk.argtypes = [I, I, I]
+        self.lib.ts_attention_biased_mma_chunk.restype = c_int
+        self.lib.ts_attention_biased_mma_scratch_floats.argtypes = [I, I, I, I, I, I]
+        self.lib.ts_attention_biased_mma_scratch_floats.restype = ctypes.c_longlong
         self.lib.ts_attention_biased_scratch_floats.argtypes = [I, I, I, I, I, I]
         self.lib.ts_attention_biased_scratch_floats.restype = ctypes.c_longlong
         self.lib.ts_rmsnorm_wide_takes_parts.argtypes = [I]
@@ -748,6 +755,28 @@ class CudaOps:
         w = 0 if window is None else int(window)
         reach = min(step.max_seq_len, w) if w else step.max_seq_len
         splits = self.biased_decode_splits
+        v_in_k = 1 if v_cache is None else 0
+        if (self.use_fast_attention and q.dtype == torch.bfloat16
+                and self.lib.ts_attention_biased_mma_supported(H, KVH, Dk, Dv, v_in_k, _code(q.dtype))):
+            # the tensor-core kernel: key rows of 64, 128 (values of the same width) or latent rows with the values inside
+            chunks = Dv // self.lib.ts_attention_biased_mma_chunk(Dk, Dv, v_in_k)
+            ms = 1
+            if step.num_decode > 0 and H // KVH <= 64:
+                ms = min(16, splits) if splits > 0 else max(1, min(16, 2 * self.num_sms // max(1, step.num_decode * KVH * chunks),
+                                                                   reach // 256))
+            scratch = counters = None
+            if ms > 1:
+                scratch = self._buffer("biased_mma_scratch", self.lib.ts_attention_biased_mma_scratch_floats(B, KVH, Dk, Dv, v_in_k, ms),
+                                       torch.float32, q.device, floor=1 << 20)
+                counters = self._buffer("biased_mma_counters", B * KVH * chunks, torch.int32, q.device, floor=1 << 14, zero=True)
+            rc = self.lib.ts_attention_biased_mma(
+                _ptr(out), out.stride(0), out.stride(1), _ptr(q), q.stride(0), q.stride(1), _ptr(k_cache), _ptr(v_cache),
+                _ptr(block_tables), _ptr(step.q_start), _ptr(step.seq_lens), B, block_tables.shape[1], step.max_q_len, H, KVH,
+                Dk, Dv, page_size, float(scale), float(softcap), _ptr(slopes), w, ms, _ptr(scratch), _ptr(counters),
+                self._stream())
+            if rc != self.UNSUPPORTED:
+                self._check(rc, "attention_biased_mma")
+                return
         if splits <= 0:
             # single-token requests: so many pieces that the chip has two blocks an SM, each with four tiles or more
             splits = 1
