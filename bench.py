@@ -724,6 +724,118 @@ def komirax_kernels(ops, z: dict, pk: dict, T: int, B: int, ctx: int, page: int)
     return out
 
 
+# ---- Pizunex (gated delta rule, attention whose values are its keys with capped and biased scores and a window,
+# latent attention) at layer sizes of real models, next to Komirax layers of the same width -----------------------
+PIZUNEX_SIZES = {
+    # width; attention heads, kv heads, head width, window; latent: heads, plain / rotated / value widths, latent sizes;
+    # delta rule: heads, query/key heads, key and value widths; dense ff (squared ReLU, no gate)
+    "1.5b": dict(width=1536, heads=12, kv_heads=2, dim=128, window=1024, lheads=12, nope=128, rope=64, lvdim=128, q_rank=768,
+                 kv_rank=512, dheads=12, dkv=6, ddim=128, dvdim=128, ff=13440, beside="1.5b"),
+    "7b": dict(width=3584, heads=28, kv_heads=4, dim=128, window=1024, lheads=28, nope=128, rope=64, lvdim=128, q_rank=1536,
+               kv_rank=512, dheads=28, dkv=14, ddim=128, dvdim=128, ff=28416, beside="7b"),
+}
+
+
+def pizunex_config(z: dict, groups: int, vocab: int):
+    """``groups`` times four layers: (attention, dense), (latent attention, dense), (delta rule, none), (delta rule, dense)."""
+    from turingserve_b200.models.pizunex import make_config
+    att = {"type": "attention", "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                                          "scale": z["dim"] ** -0.5, "softcap": 50.0, "mask": {"size": z["window"]},
+                                          "q_temp": {"coef": 0.3, "every": 64}}}
+    lat = {"type": "latent_attention",
+           "mixer": {"heads": z["lheads"], "dim": z["nope"], "rot_dim": z["rope"], "vdim": z["lvdim"], "q_rank": z["q_rank"],
+                     "kv_rank": z["kv_rank"], "scale": (z["nope"] + z["rope"]) ** -0.5,
+                     "rot": {"base": 10000.0, "dims": z["rope"],
+                             "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    dlt = {"type": "delta", "mixer": {"heads": z["dheads"], "kv_heads": z["dkv"], "dim": z["ddim"], "vdim": z["dvdim"], "conv": 4}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    four = [{**att, "mlp": dense}, {**lat, "mlp": dense}, {**dlt, "mlp": None}, {**dlt, "mlp": dense}]
+    return make_config(width=z["width"], vocab=vocab, layers=four * groups, eps=1e-6)
+
+
+def pizunex_kernels(ops, z: dict, pk: dict, T: int, B: int, ctx: int, page: int) -> dict:
+    """Each kernel of the new mechanisms alone: a portion of T tokens and B single tokens at context ``ctx``."""
+    import torch
+    from types import SimpleNamespace
+    dev = torch.device("cuda", 0)
+    big = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    flush = lambda: big.fill_(1)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    out = {}
+    FP32_PEAK = 148 * 128 * 2 * 1.965e9                      # FFMA lanes x 2 x the highest SM clock: nominal
+    hbm = pk["hbm_gbs"] * 1e9
+    bf = torch.bfloat16
+
+    # the delta rule: prepare (filter, unit length, gates) and the scan
+    H, G, D, V, taps = z["dheads"], z["dkv"], z["ddim"], z["dvdim"], 4
+    C = 2 * G * D + H * V
+    for name, rows, reqs in (("prefill", T, 1), ("decode", B, B)):
+        per = rows // reqs
+        proj = torch.randn(rows, C + H * V + 2 * H, device=dev).to(bf)
+        conv_w = torch.randn(C, taps, device=dev) * 0.5
+        a_log, dt = torch.zeros(H, device=dev), torch.zeros(H, device=dev)
+        state = torch.zeros(reqs + 1, H * D * V + (taps - 1) * C, device=dev)
+        ready = torch.empty(rows, C + 2 * H + G, device=dev)
+        o = torch.empty(rows, H * V, device=dev)
+        step = SimpleNamespace(q_start=i32([i * per for i in range(reqs + 1)]), state_slots=i32(list(range(reqs))),
+                               num_requests=reqs, token_request=i32([r for r in range(reqs) for _ in range(per)]))
+        ms_p = timed(lambda: ops.delta_prepare(ready, proj, conv_w, a_log, dt, state, step, H, G, D, V, taps, 1e-6), flush)
+        ms = timed(lambda: ops.delta_scan(o, ready, proj, state, step, H, G, D, V, taps), flush)
+        flops = 8.0 * rows * H * D * V                       # two sums, the decay and the write, 2 operations each
+        byts = 2.0 * reqs * H * D * V * 4 + rows * (2 * G * D + H * V + 2 * H + G) * 4 + rows * H * V * 4
+        out[f"delta_scan_{name}"] = {"us": round(ms * 1e3, 1), "prepare_us": round(ms_p * 1e3, 1),
+                                     "tflops_fp32": round(flops / ms / 1e9, 2),
+                                     "frac_of_fp32_ffma_nominal": round(flops / (ms / 1e3) / FP32_PEAK, 3),
+                                     "frac_of_hbm": round(byts / (ms / 1e3) / hbm, 3)}
+
+    def tables_for(reqs, seq, width):
+        t = torch.zeros(reqs, width, dtype=torch.int32, device=dev)
+        n = -(-seq // page)
+        for r in range(reqs):
+            t[r, :n] = torch.arange(1 + r * n, 1 + (r + 1) * n, dtype=torch.int32, device=dev)
+        return t
+
+    pages = B * (-(-(ctx + 1) // page)) + -(-T // page) + 2
+    width = -(-max(ctx + 1, T) // page)
+    # attention with capped, biased scores and a window; values of the keys' width
+    H, G, D, win = z["heads"], z["kv_heads"], z["dim"], z["window"]
+    kc = torch.randn(pages, G, page, D, device=dev).to(bf)
+    vc = torch.randn(pages, G, page, D, device=dev).to(bf)
+    slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], device=dev)
+    for name, reqs, per, seq in (("prefill", 1, T, T), ("decode", B, 1, ctx + 1)):
+        rows = reqs * per
+        q = torch.randn(rows, H, D, device=dev).to(bf)
+        o = torch.empty(rows, H, D, dtype=bf, device=dev)
+        step = SimpleNamespace(q_start=i32([i * per for i in range(reqs + 1)]), seq_lens=i32([seq] * reqs), num_requests=reqs,
+                               num_decode=reqs if per == 1 else 0, max_q_len=per, max_seq_len=seq)
+        bt = tables_for(reqs, seq, width)
+        ms = timed(lambda: ops.attention_biased(o, q, kc, vc, bt, step, G, page, D ** -0.5, 50.0, slopes, win), flush)
+        seen = sum(min(i + 1, win) for i in range(seq - per, seq))       # keys a request's queries see
+        flops = 4.0 * D * H * seen * reqs
+        byts = reqs * min(seq, win + per) * G * 2 * D * 2.0
+        out[f"capped_attention_{name}"] = {"us": round(ms * 1e3, 1), "tflops": round(flops / ms / 1e9, 1),
+                                           "frac_of_bf16": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 3),
+                                           "frac_of_hbm": round(byts / (ms / 1e3) / hbm, 3)}
+    # latent attention: every head over the one cached row a token (keys of kv_rank + rot_dim, values its first kv_rank)
+    H, rank, R = z["lheads"], z["kv_rank"], z["rope"]
+    kc = torch.randn(pages, 1, page, rank + R, device=dev).to(bf)
+    for name, reqs, per, seq in (("prefill", 1, T, T), ("decode", B, 1, ctx + 1)):
+        rows = reqs * per
+        q = torch.randn(rows, H, rank + R, device=dev).to(bf)
+        o = torch.empty(rows, H, rank, dtype=bf, device=dev)
+        step = SimpleNamespace(q_start=i32([i * per for i in range(reqs + 1)]), seq_lens=i32([seq] * reqs), num_requests=reqs,
+                               num_decode=reqs if per == 1 else 0, max_q_len=per, max_seq_len=seq)
+        bt = tables_for(reqs, seq, width)
+        ms = timed(lambda: ops.attention_biased(o, q, kc, None, bt, step, 1, page, 0.07, 0.0, None, None), flush)
+        seen = sum(i + 1 for i in range(seq - per, seq))
+        flops = 2.0 * (2 * rank + R) * H * seen * reqs      # scores over rank + R columns, values over rank
+        byts = reqs * seq * (rank + R) * 2.0
+        out[f"latent_attention_{name}"] = {"us": round(ms * 1e3, 1), "tflops": round(flops / ms / 1e9, 1),
+                                           "frac_of_bf16": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 3),
+                                           "frac_of_hbm": round(byts / (ms / 1e3) / hbm, 3)}
+    return out
+
+
 def run_design(a) -> dict:
     """``--design komirax``: prefill and decode throughput of Komirax layers beside Qwen2 layers of the same
     width and count (random weights, bfloat16, through the step function), and each new kernel alone."""
@@ -740,7 +852,7 @@ def run_design(a) -> dict:
     B, T, ctx, page = a.batch, a.prefill_tokens, a.prompt_len, 64
     steps, warmup = min(a.steps, 64), max(3, a.warmup)
     vocab = 32768
-    result = {"design": "komirax", "dtype": "bfloat16", "data": "synthetic", "peaks": pk_src, "batch": B,
+    result = {"design": a.design, "dtype": "bfloat16", "data": "synthetic", "peaks": pk_src, "batch": B,
               "prefill_tokens": T, "context": ctx, "page": page, "sizes": {}}
 
     def measure(eng):
@@ -778,9 +890,31 @@ def run_design(a) -> dict:
                 "decode_tok_s": round(B / (dms / 1e3), 1)}
 
     for name in a.design_sizes.split(","):
-        z = KOMIRAX_SIZES[name]
         groups = a.layers // 4 if a.layers else 2
         ctx_len = max(ctx + warmup + steps + 64, T + 64)
+        if a.design == "pizunex":
+            # beside Komirax layers of the same width, the closest design the engine has (a 32-bit stream, a recurrent
+            # mixer with a matrix state, an attention of its own, feed-forwards without a gate)
+            z = PIZUNEX_SIZES[name]
+            eng = build_engine_on_device(f"pizunex-{name}", 4 * groups, ctx_len=ctx_len, page=page, max_seqs=B,
+                                         max_tokens=max(T, ctx), graph_sizes=(B,), mcfg=pizunex_config(z, groups, vocab))
+            ours = measure(eng)
+            del eng
+            torch.cuda.empty_cache()
+            eng = build_engine_on_device(f"komirax-{z['beside']}", 4 * groups, ctx_len=ctx_len, page=page, max_seqs=B,
+                                         max_tokens=max(T, ctx), graph_sizes=(B,),
+                                         mcfg=komirax_config(KOMIRAX_SIZES[z["beside"]], groups, vocab))
+            beside = measure(eng)
+            del eng
+            torch.cuda.empty_cache()
+            entry = {"layers": 4 * groups, "width": z["width"], "pizunex": ours, "beside": f"komirax-{z['beside']}", "komirax": beside,
+                     "prefill_ratio": round(ours["prefill_tok_s"] / beside["prefill_tok_s"], 3),
+                     "decode_ratio": round(ours["decode_tok_s"] / beside["decode_tok_s"], 3)}
+            if "kernels" in a.phases.split(","):
+                entry["kernels"] = pizunex_kernels(ops, z, pk, T, B, ctx, page)
+            result["sizes"][name] = entry
+            continue
+        z = KOMIRAX_SIZES[name]
         kcfg = komirax_config(z, groups, vocab)
         eng = build_engine_on_device(f"komirax-{name}", 4 * groups, ctx_len=ctx_len, page=page, max_seqs=B,
                                      max_tokens=max(T, ctx), graph_sizes=(B,), mcfg=kcfg)
@@ -887,8 +1021,9 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--phases", default="prefill,decode,points,e2e,kernels,mixed",
                     help="which measurements to run (decode always runs); fewer for a profiler capture")
-    ap.add_argument("--design", default="", choices=["", "komirax"],
-                    help="instead of the default workload: layers of this design beside Qwen2 layers of the same width "
+    ap.add_argument("--design", default="", choices=["", "komirax", "pizunex"],
+                    help="instead of the default workload: layers of this design beside layers of the closest other one (Komirax "
+                         "beside Qwen2, Pizunex beside Komirax) at the same width "
                          "(prefill and decode throughput, and each of the design's kernels alone)")
     ap.add_argument("--design-sizes", default="1.5b,7b", help="which of the design's layer sizes to run")
     a = ap.parse_args()

@@ -10,7 +10,8 @@
 //     few 1e-7 of the cap) and biased there; the softmax weights stay 32-bit in the sums and enter the second
 //     product as TWO bfloat16 terms (p = hi + lo, two products), so they carry 16 bits of mantissa, not 8;
 //   * wide value rows are cut into chunks of DV columns, one block each (a block's accumulator is 16 x DV per warp):
-//     a latent row of 512 value columns is four blocks that each redo the scores;
+//     a latent row of 512 value columns is two blocks that each redo the scores (128 accumulator registers a thread:
+//     the shared memory of a 576-wide tile allows one block an SM anyway);
 //   * requests that bring ONE token may have their keys cut over `splits` blocks; each leaves (m, l, unnormalised
 //     sum) in scratch and the block that comes last (a ticket counter; nobody waits) merges them in split order.
 #include "common.cuh"
@@ -60,7 +61,6 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
   unsigned char* k_s = q_s + BM_ROWS * DK * 2;                       // [STAGES][64][DK]
   unsigned char* v_s = k_s + STAGES * BM_TILE * DK * 2;              // [STAGES][64][DV] (absent when the values are in the key rows)
   __shared__ int pages_s[BM_PAGES_S];
-  __shared__ float w_s[BM_ROWS][BM_MAX_SPLITS];
   __shared__ int last_flag;
 
   // this thread's two rows
@@ -300,29 +300,45 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
   __syncthreads();
   if (!last_flag) return;
   __threadfence();
+  // The merge, by the block that came last.  Every load of another block's numbers is independent of the others and
+  // issued before any is used: a chain of dependent L2 round trips, one a split, would cost more than the attention.
   const float* all = scratch + group * BM_ROWS * REC;
+  float* m_m = reinterpret_cast<float*>(smem);                       // [64][16] maxima, then weights (the tiles are done with)
+  float* l_m = m_m + BM_ROWS * BM_MAX_SPLITS;                        // [64][16] sums
+  for (int idx = threadIdx.x; idx < n_rows * my_splits; idx += BM_WARPS * 32) {
+    const int row = idx / my_splits, sp = idx % my_splits;
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(all + ((size_t)sp * BM_ROWS + row) * REC));
+    m_m[row * BM_MAX_SPLITS + sp] = ml.x;
+    l_m[row * BM_MAX_SPLITS + sp] = ml.y;
+  }
+  __syncthreads();
   for (int row = threadIdx.x; row < n_rows; row += BM_WARPS * 32) {
     float mm = -INFINITY;
-    for (int sp = 0; sp < my_splits; ++sp) mm = fmaxf(mm, __ldcg(all + ((size_t)sp * BM_ROWS + row) * REC));
+    for (int sp = 0; sp < my_splits; ++sp) mm = fmaxf(mm, m_m[row * BM_MAX_SPLITS + sp]);
     float ll = 0.f;
     for (int sp = 0; sp < my_splits; ++sp) {
-      const float* part = all + ((size_t)sp * BM_ROWS + row) * REC;
-      const float pm = __ldcg(part);
+      const float pm = m_m[row * BM_MAX_SPLITS + sp];
       const float w = pm == -INFINITY ? 0.f : exp2f(pm - mm);
-      w_s[row][sp] = w;
-      ll = fmaf(__ldcg(part + 1), w, ll);
+      m_m[row * BM_MAX_SPLITS + sp] = w;
+      ll = fmaf(l_m[row * BM_MAX_SPLITS + sp], w, ll);
     }
     const float inv = ll > 0.f ? 1.f / ll : 0.f;
-    for (int sp = 0; sp < my_splits; ++sp) w_s[row][sp] *= inv;
+    for (int sp = 0; sp < my_splits; ++sp) m_m[row * BM_MAX_SPLITS + sp] *= inv;
   }
   __syncthreads();
   for (int idx = threadIdx.x; idx < n_rows * (DV / 2); idx += BM_WARPS * 32) {
     const int row = idx / (DV / 2), d = (idx % (DV / 2)) * 2;
+    float2 v[BM_MAX_SPLITS];
+#pragma unroll
+    for (int sp = 0; sp < BM_MAX_SPLITS; ++sp)
+      v[sp] = sp < my_splits ? __ldcg(reinterpret_cast<const float2*>(all + ((size_t)sp * BM_ROWS + row) * REC + 2 + d))
+                             : make_float2(0.f, 0.f);
     float a0 = 0.f, a1 = 0.f;
-    for (int sp = 0; sp < my_splits; ++sp) {
-      const float2 v = __ldcg(reinterpret_cast<const float2*>(all + ((size_t)sp * BM_ROWS + row) * REC + 2 + d));
-      a0 = fmaf(v.x, w_s[row][sp], a0);
-      a1 = fmaf(v.y, w_s[row][sp], a1);
+#pragma unroll
+    for (int sp = 0; sp < BM_MAX_SPLITS; ++sp) {
+      const float w = sp < my_splits ? m_m[row * BM_MAX_SPLITS + sp] : 0.f;
+      a0 = fmaf(v[sp].x, w, a0);
+      a1 = fmaf(v[sp].y, w, a1);
     }
     bf16* dst = out + (size_t)qs * out_ts + (size_t)(kvh * G + row) * out_hs + chunk * DV + d;
     *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(a0, a1);
@@ -368,7 +384,7 @@ TS_API int ts_attention_biased_mma_supported(int H, int KVH, int Dk, int Dv, int
 // Columns of the value rows one block takes (the value rows are cut into Dv / this chunks).
 TS_API int ts_attention_biased_mma_chunk(int Dk, int Dv, int v_in_k) {
   const int i = instance_of(Dk, Dv, v_in_k);
-  return i == 0 ? 0 : (i <= 2 ? Dv : 128);
+  return i == 0 ? 0 : (i <= 2 ? Dv : 256);
 }
 
 TS_API long long ts_attention_biased_mma_scratch_floats(int B, int KVH, int Dk, int Dv, int v_in_k, int splits) {
@@ -401,7 +417,7 @@ TS_API int ts_attention_biased_mma(void* out, int out_ts, int out_hs, const void
                                   page, scale, softcap, slopes, window, CHUNKS, splits, scratch, counters, s)
   if (inst == 1) TS_BM(64, 64, false, 3, 1);
   if (inst == 2) TS_BM(128, 128, false, 3, 1);
-  if (inst == 3) TS_BM(576, 128, true, 2, 4);
-  TS_BM(320, 128, true, 3, 2);
+  if (inst == 3) TS_BM(576, 256, true, 2, 2);
+  TS_BM(320, 256, true, 3, 1);
 #undef TS_BM
 }

@@ -6,24 +6,25 @@
 // filter's last taps - 1 inputs are kept behind S in the same slot: [H D V | (taps - 1) x C], C = 2 G D + H V.
 //
 // Three kernels:
-//   ts_delta_prepare      one block a token: filter + SiLU, unit length per head, g, beta and k.q, as 32-bit
+//   ts_delta_prepare      one block per (token, head): filter + SiLU, unit length per head, g, beta and k.q, as 32-bit
 //                         rows [q (G D) | k (G D) | v (H V) | g (H) | beta (H) | k.q (G)]; reads the slot's filter
 //                         inputs for the tokens before the step's first, writes nothing to the slot
 //   ts_delta_scan         the recurrence, token by token for portions and single tokens alike (cutting a prompt
-//                         changes no bit); afterwards one block a request stores the filter's new last inputs
+//                         changes no bit); afterwards the request's blocks store the filter's new last inputs
 //   ts_head_gated_rmsnorm o / rms(o) per head, times a weight shared by the heads, times silu(gate)
 //
 // The scan: one pass over the state per token.  With a = (g S)^T k and c = (g S)^T q, both sums over the old
 // state, u = beta (v - a) and o = c + (k.q) u, so the read-out needs no second pass after the write.  A column
 // of S is independent of the others: P lanes of one warp hold it (R rows each, in registers over all tokens of
 // the step), the two sums cross the P lanes by shuffles, and no block-wide barrier sits inside a token.  Tokens
-// arrive in groups of DR_GROUP rows by cp.async while the group before is computed.
+// arrive in groups of DR_GROUP rows by cp.async, three groups ahead of the one that is computed.
 #include "common.cuh"
 #include "mma_utils.cuh"
 
 namespace {
 
 constexpr int DR_GROUP = 16;     // tokens staged at a time
+constexpr int DR_STAGES = 4;     // groups in flight or in use: the rows of three groups are on their way while one is computed
 constexpr int DR_PAD = 4;        // floats between two lanes' row pieces in shared memory (bank spread)
 
 __device__ __forceinline__ void cp_async_4(void* smem, const void* gmem) {
@@ -41,55 +42,60 @@ delta_prepare_kernel(float* __restrict__ ready, const T* __restrict__ proj, int 
                      const int* __restrict__ slots, int H, int G, int D, int V, int taps, float unit_eps) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float f_s[];                       // [C] filtered and activated channels
-  const int t = blockIdx.x;
+  extern __shared__ float f_s[];                       // [2 D] filtered and activated q and k of one head
+  __shared__ float scratch[32];
+  const int t = blockIdx.x, unit = blockIdx.y;         // units: the G query/key heads, then the H value heads
   const int b = token_request[t];
   const int t0 = q_start[b], i = t - t0;
   const int qk = G * D, hv = H * V, C = 2 * qk + hv, W = C + 2 * H + G;
   const float* tail = state + (size_t)slots[b] * state_stride + (size_t)H * D * V;     // [taps - 1][C]
   float* out = ready + (size_t)t * W;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+  auto filtered = [&](int c) {
     float acc = 0.f;
     for (int u = 0; u < taps; ++u) {
       const int rel = i - (taps - 1) + u;              // the input's place, counted from the step's first token
       const float x = rel >= 0 ? to_f(proj[(size_t)(t0 + rel) * proj_stride + c]) : tail[(size_t)(rel + taps - 1) * C + c];
       acc = fmaf(conv_w[c * taps + u], x, acc);
     }
-    const float y = acc / (1.f + expf(-acc));
-    f_s[c] = y;
-    if (c >= 2 * qk) out[c] = y;
-  }
-  __syncthreads();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  const float inv_sqrt_d = 1.f / sqrtf((float)D);
-  for (int g = warp; g < G; g += nwarps) {
-    const float* fq = f_s + g * D;
-    const float* fk = f_s + qk + g * D;
-    float sq = 0.f, sk = 0.f, dot = 0.f;
-    for (int d = lane; d < D; d += 32) {
-      sq = fmaf(fq[d], fq[d], sq);
-      sk = fmaf(fk[d], fk[d], sk);
-      dot = fmaf(fq[d], fk[d], dot);
+    return acc / (1.f + expf(-acc));
+  };
+  if (unit >= G) {
+    const int h = unit - G;
+    for (int d = threadIdx.x; d < V; d += blockDim.x) out[2 * qk + h * V + d] = filtered(2 * qk + h * V + d);
+    if (h == 0) {
+      for (int hh = threadIdx.x; hh < H; hh += blockDim.x) {
+        const T* row = proj + (size_t)t * proj_stride + C + hv;
+        const float bb = to_f(row[hh]), aa = to_f(row[H + hh]);
+        out[C + hh] = expf(-expf(a_log[hh]) * softplus_f(aa + dt_bias[hh]));
+        out[C + H + hh] = 1.f / (1.f + expf(-bb));
+      }
     }
-    sq = warp_sum(sq), sk = warp_sum(sk), dot = warp_sum(dot);
-    const float rq = inv_sqrt_d / sqrtf(sq + unit_eps), rk = 1.f / sqrtf(sk + unit_eps);
-    for (int d = lane; d < D; d += 32) {
-      out[g * D + d] = fq[d] * rq;
-      out[qk + g * D + d] = fk[d] * rk;
-    }
-    if (lane == 0) out[C + 2 * H + g] = dot * rq * rk;
+    return;
   }
-  for (int h = threadIdx.x; h < H; h += blockDim.x) {
-    const T* row = proj + (size_t)t * proj_stride + C + hv;
-    const float bb = to_f(row[h]), aa = to_f(row[H + h]);
-    out[C + h] = expf(-expf(a_log[h]) * softplus_f(aa + dt_bias[h]));
-    out[C + H + h] = 1.f / (1.f + expf(-bb));
+  const int g = unit;
+  float sq = 0.f, sk = 0.f, dot = 0.f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    const float fq = filtered(g * D + d), fk = filtered(qk + g * D + d);
+    f_s[d] = fq;
+    f_s[D + d] = fk;
+    sq = fmaf(fq, fq, sq);
+    sk = fmaf(fk, fk, sk);
+    dot = fmaf(fq, fk, dot);
   }
+  sq = block_sum(sq, scratch);
+  sk = block_sum(sk, scratch);
+  dot = block_sum(dot, scratch);
+  const float rq = 1.f / (sqrtf((float)D) * sqrtf(sq + unit_eps)), rk = 1.f / sqrtf(sk + unit_eps);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {  // (a thread reads back what it wrote itself)
+    out[g * D + d] = f_s[d] * rq;
+    out[qk + g * D + d] = f_s[D + d] * rk;
+  }
+  if (threadIdx.x == 0) out[C + 2 * H + g] = dot * rq * rk;
 }
 
 // R rows of a column a lane; P lanes a column; CW = 32 / P columns a warp.
 template <int R>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 1)
 delta_scan_kernel(float* __restrict__ out, const float* __restrict__ ready, const void* __restrict__ proj,
                   int proj_stride, int proj_is_bf16, float* __restrict__ state, size_t state_stride,
                   const int* __restrict__ q_start, const int* __restrict__ slots, int H, int G, int D, int V,
@@ -120,56 +126,63 @@ delta_scan_kernel(float* __restrict__ out, const float* __restrict__ ready, cons
     const int d = p * R + i;
     s[i] = (live && d < D) ? S[(size_t)d * V + j] : 0.f;
   }
-  for (int i = threadIdx.x; i < 2 * DR_GROUP * tok_w; i += blockDim.x) smem[i] = 0.f;   // (rows beyond D stay zero)
+  for (int i = threadIdx.x; i < DR_STAGES * DR_GROUP * tok_w; i += blockDim.x) smem[i] = 0.f;   // (rows beyond D stay zero)
   __syncthreads();
 
+  // a warp brings whole tokens, its lanes the pieces of a row: additions and shifts only (a lane's copies follow one
+  // another in a chain of dependent index arithmetic, so a division per copy would cost more than the scan itself)
   auto fetch = [&](int g0, int buf) {
     const int gn = min(DR_GROUP, n - g0);
     float* dst0 = smem + (size_t)buf * DR_GROUP * tok_w;
-    if (vec4) {
-      const int chunks = D / 4, per_tok = 2 * chunks;
-      for (int i = threadIdx.x; i < gn * per_tok; i += blockDim.x) {
-        const int r = i / per_tok, c = i % per_tok;
-        const int which = c >= chunks, d = (which ? c - chunks : c) * 4;
-        const float* src = ready + (size_t)(t0 + g0 + r) * W + which * qk + kvh * D + d;
-        cp_async_16(dst0 + r * tok_w + which * row_w + (d / R) * (R + DR_PAD) + d % R, src, true);
-      }
-    } else {
-      for (int i = threadIdx.x; i < gn * 2 * D; i += blockDim.x) {
-        const int r = i / (2 * D), c = i % (2 * D);
-        const int which = c >= D, d = which ? c - D : c;
-        const float* src = ready + (size_t)(t0 + g0 + r) * W + which * qk + kvh * D + d;
-        cp_async_4(dst0 + r * tok_w + which * row_w + (d / R) * (R + DR_PAD) + d % R, src);
-      }
-    }
-    for (int i = threadIdx.x; i < gn * (cols_block + 3); i += blockDim.x) {
-      const int r = i / (cols_block + 3), c = i % (cols_block + 3);
+    for (int r = warp; r < gn; r += nwarps) {
       const float* row = ready + (size_t)(t0 + g0 + r) * W;
-      float* dst = dst0 + r * tok_w + 2 * row_w + c;
-      if (c < cols_block) {
-        const int jj = blockIdx.x * cols_block + c;
-        if (jj < V) cp_async_4(dst, row + 2 * qk + h * V + jj);
-      } else if (c == cols_block) cp_async_4(dst, row + C + h);
-      else if (c == cols_block + 1) cp_async_4(dst, row + C + H + h);
-      else cp_async_4(dst, row + C + 2 * H + kvh);
+      const float* qrow = row + kvh * D;
+      const float* krow = row + qk + kvh * D;
+      float* dst = dst0 + r * tok_w;
+      if (vec4) {
+        for (int d = lane * 4; d < D; d += 128) {
+          const int off = (d / R) * (R + DR_PAD) + d % R;          // (R is a power of two)
+          cp_async_16(dst + off, qrow + d, true);
+          cp_async_16(dst + row_w + off, krow + d, true);
+        }
+      } else {
+        for (int d = lane; d < D; d += 32) {
+          const int off = (d / R) * (R + DR_PAD) + d % R;
+          cp_async_4(dst + off, qrow + d);
+          cp_async_4(dst + row_w + off, krow + d);
+        }
+      }
+      float* tail_dst = dst + 2 * row_w;
+      for (int c = lane; c < cols_block + 3; c += 32) {
+        if (c < cols_block) {
+          const int jj = blockIdx.x * cols_block + c;
+          if (jj < V) cp_async_4(tail_dst + c, row + 2 * qk + h * V + jj);
+        } else if (c == cols_block) cp_async_4(tail_dst + c, row + C + h);
+        else if (c == cols_block + 1) cp_async_4(tail_dst + c, row + C + H + h);
+        else cp_async_4(tail_dst + c, row + C + 2 * H + kvh);
+      }
     }
   };
 
-  fetch(0, 0);
-  cp_async_commit();
-  int buf = 0;
-  for (int g0 = 0; g0 < n; g0 += DR_GROUP, buf ^= 1) {
-    const int gn = min(DR_GROUP, n - g0);
-    if (g0 + DR_GROUP < n) fetch(g0 + DR_GROUP, buf ^ 1);
+#pragma unroll
+  for (int st = 0; st < DR_STAGES - 1; ++st) {
+    if (st * DR_GROUP < n) fetch(st * DR_GROUP, st);
     cp_async_commit();
-    cp_async_wait<1>();
+  }
+  int buf = 0;
+  for (int g0 = 0; g0 < n; g0 += DR_GROUP, buf = (buf + 1) % DR_STAGES) {
+    const int gn = min(DR_GROUP, n - g0);
+    // (the buffer filled now is the one the group before this one was computed from: the barrier at its end freed it)
+    if (g0 + (DR_STAGES - 1) * DR_GROUP < n) fetch(g0 + (DR_STAGES - 1) * DR_GROUP, (buf + DR_STAGES - 1) % DR_STAGES);
+    cp_async_commit();
+    cp_async_wait<DR_STAGES - 1>();
     __syncthreads();                                           // this group's rows are here
     const float* grp = smem + (size_t)buf * DR_GROUP * tok_w;
     for (int r = 0; r < gn; ++r) {
       const float* tok = grp + r * tok_w;
       const float4* qr = reinterpret_cast<const float4*>(tok + p * (R + DR_PAD));
       const float4* kr = reinterpret_cast<const float4*>(tok + row_w + p * (R + DR_PAD));
-      float a0 = 0.f, a1 = 0.f, c0 = 0.f, c1 = 0.f;
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;   // eight chains of R / 4
 #pragma unroll
       for (int i = 0; i < R / 4; ++i) {
         const float4 k4 = kr[i], q4 = qr[i];
@@ -177,12 +190,12 @@ delta_scan_kernel(float* __restrict__ out, const float* __restrict__ ready, cons
         c0 = fmaf(s[4 * i + 0], q4.x, c0);
         a1 = fmaf(s[4 * i + 1], k4.y, a1);
         c1 = fmaf(s[4 * i + 1], q4.y, c1);
-        a0 = fmaf(s[4 * i + 2], k4.z, a0);
-        c0 = fmaf(s[4 * i + 2], q4.z, c0);
-        a1 = fmaf(s[4 * i + 3], k4.w, a1);
-        c1 = fmaf(s[4 * i + 3], q4.w, c1);
+        a2 = fmaf(s[4 * i + 2], k4.z, a2);
+        c2 = fmaf(s[4 * i + 2], q4.z, c2);
+        a3 = fmaf(s[4 * i + 3], k4.w, a3);
+        c3 = fmaf(s[4 * i + 3], q4.w, c3);
       }
-      float a = a0 + a1, c = c0 + c1;
+      float a = (a0 + a1) + (a2 + a3), c = (c0 + c1) + (c2 + c3);
       for (int off = CW; off < 32; off <<= 1) {
         a += __shfl_xor_sync(0xffffffffu, a, off);
         c += __shfl_xor_sync(0xffffffffu, c, off);
@@ -210,26 +223,27 @@ delta_scan_kernel(float* __restrict__ out, const float* __restrict__ ready, cons
     if (live && d < D) S[(size_t)d * V + j] = s[i];
   }
   // the filter's new last inputs: what the slot held, moved up by n, then this step's raw rows
-  if (blockIdx.x == 0 && h == 0 && taps > 1) {
+  if (taps > 1) {
     float* tail = base + (size_t)H * D * V;
-    for (int c = threadIdx.x; c < C; c += blockDim.x) {
-      float nv[8];
+    const int first = (h * gridDim.x + blockIdx.x) * blockDim.x + threadIdx.x, stride = H * gridDim.x * blockDim.x;
+    for (int c = first; c < C; c += stride) {                  // every block of the request takes a share of the channels
+      float nv[7];
 #pragma unroll
       for (int jt = 0; jt < 7; ++jt) {
-        if (jt >= taps - 1) break;
         const int rel = n - (taps - 1) + jt;
-        if (rel >= 0) {
-          const size_t at = (size_t)(t0 + rel) * proj_stride + c;
-          nv[jt] = proj_is_bf16 ? to_f(reinterpret_cast<const bf16*>(proj)[at]) : reinterpret_cast<const float*>(proj)[at];
-        } else {
-          nv[jt] = tail[(size_t)(rel + taps - 1) * C + c];
+        nv[jt] = 0.f;
+        if (jt < taps - 1) {
+          if (rel >= 0) {
+            const size_t at = (size_t)(t0 + rel) * proj_stride + c;
+            nv[jt] = proj_is_bf16 ? to_f(reinterpret_cast<const bf16*>(proj)[at]) : reinterpret_cast<const float*>(proj)[at];
+          } else {
+            nv[jt] = tail[(size_t)(rel + taps - 1) * C + c];
+          }
         }
       }
 #pragma unroll
-      for (int jt = 0; jt < 7; ++jt) {
-        if (jt >= taps - 1) break;
-        tail[(size_t)jt * C + c] = nv[jt];
-      }
+      for (int jt = 0; jt < 7; ++jt)
+        if (jt < taps - 1) tail[(size_t)jt * C + c] = nv[jt];
     }
   }
 }
@@ -256,7 +270,12 @@ head_gated_rmsnorm_kernel(T* __restrict__ out, const float* __restrict__ x, cons
   }
 }
 
+int g_delta_rows = 0;
+
 }  // namespace
+
+// Rows of a state column a lane of the scan holds (8, 16 or 32; 0: by the key width).  For measurements.
+TS_API void ts_set_delta_rows(int rows) { g_delta_rows = rows; }
 
 // ready: [T, 2 G D + H V + 2 H + G] 32-bit.  proj: [T, proj_stride] rows holding q at column 0, k at G D, v at
 // 2 G D, then the gate (H V), b (H) and a (H).  conv_w: [2 G D + H V, taps] 32-bit.  state: [slots, state_stride].
@@ -267,8 +286,9 @@ TS_API int ts_delta_prepare(float* ready, const void* proj, int proj_stride, con
   if (T <= 0) return 0;
   if (H <= 0 || G <= 0 || H % G || D <= 0 || V <= 0) TS_REFUSE(TS_ERR_SHAPE, "ts_delta_prepare: %d heads over %d of %d x %d", H, G, D, V);
   if (taps < 1 || taps > 8) TS_REFUSE(TS_ERR_LIMIT, "ts_delta_prepare: %d taps (1 to 8)", taps);
-  const size_t smem = sizeof(float) * ((size_t)2 * G * D + (size_t)H * V);
-  if (smem > 200 * 1024) TS_REFUSE(TS_ERR_LIMIT, "ts_delta_prepare: %zu filtered channels", smem / 4);
+  const size_t smem = sizeof(float) * (size_t)2 * D;
+  if (smem > 200 * 1024) TS_REFUSE(TS_ERR_LIMIT, "ts_delta_prepare: keys of %d", D);
+  if (G + H > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_delta_prepare: %d heads", G + H);
   cudaStream_t s = (cudaStream_t)stream;
 #define TS_DP(TT)                                                                                                        \
   do {                                                                                                                   \
@@ -278,7 +298,7 @@ TS_API int ts_delta_prepare(float* ready, const void* proj, int proj_stride, con
       if (e != cudaSuccess) TS_REFUSE((int)e, "ts_delta_prepare: shared memory %zu: %s", smem, cudaGetErrorString(e));   \
       configured = smem;                                                                                                 \
     }                                                                                                                    \
-    ts_launch(delta_prepare_kernel<TT>, dim3(T), dim3(128), smem, s, ready, (const TT*)proj, proj_stride, conv_w, a_log, \
+    ts_launch(delta_prepare_kernel<TT>, dim3(T, G + H), dim3(128), smem, s, ready, (const TT*)proj, proj_stride, conv_w, a_log, \
               dt_bias, state, (size_t)state_stride, token_request, q_start, slots, H, G, D, V, taps, unit_eps);          \
   } while (0)
   if (dtype == TS_F32) TS_DP(float);
@@ -297,16 +317,22 @@ TS_API int ts_delta_scan(float* out, const float* ready, const void* proj, int p
   if (taps < 1 || taps > 8) TS_REFUSE(TS_ERR_LIMIT, "ts_delta_scan: %d taps (1 to 8)", taps);
   if (dtype != TS_F32 && dtype != TS_BF16) TS_REFUSE(TS_ERR_DTYPE, "ts_delta_scan: dtype %d", dtype);
   if (B > 65535 || H > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_delta_scan: %d requests / %d heads per launch", B, H);
-  const int R = D > 64 ? 32 : 16;
+  // rows of a column a lane holds: few rows mean more lanes a column, so more warps to hide one another's latencies
+  // (one warp a scheduler waits out every dependent instruction), but a longer shuffle tree
+  int R = g_delta_rows;
+  if (R != 8 && R != 16 && R != 32) R = D <= 256 ? 8 : (D <= 512 ? 16 : 32);
+  while (R < 32 && R * 32 < D) R *= 2;
   int P = 1;
   while (P * R < D) P <<= 1;
   if (P > 32) TS_REFUSE(TS_ERR_LIMIT, "ts_delta_scan: keys of %d (limit 1024)", D);
   const int CW = 32 / P;
-  const int nwarps = min(8, ceil_div(V, CW));
+  // 16 columns a block (or what a warp holds, if that is more): a portion of one request has H x V / 16 blocks to
+  // spread over the chip, and every block stages the same q and k rows out of L2
+  const int nwarps = max(1, min(8, min(ceil_div(16, CW), ceil_div(V, CW))));
   const int cols_block = nwarps * CW;
   const int W = 2 * G * D + H * V + 2 * H + G;
   const int vec4 = D % 4 == 0 && W % 4 == 0 && (G * D) % 4 == 0 && !((uintptr_t)ready & 15);
-  const size_t smem = sizeof(float) * 2 * DR_GROUP * ((size_t)2 * P * (R + DR_PAD) + ((cols_block + 3 + 3) & ~3));
+  const size_t smem = sizeof(float) * DR_STAGES * DR_GROUP * ((size_t)2 * P * (R + DR_PAD) + ((cols_block + 3 + 3) & ~3));
   if (smem > 200 * 1024) TS_REFUSE(TS_ERR_LIMIT, "ts_delta_scan: shared memory %zu", smem);
   cudaStream_t s = (cudaStream_t)stream;
   dim3 grid(ceil_div(V, cols_block), H, B);
@@ -322,7 +348,8 @@ TS_API int ts_delta_scan(float* out, const float* ready, const void* proj, int p
               dtype == TS_BF16 ? 1 : 0, state, (size_t)state_stride, q_start, slots, H, G, D, V, taps, P, vec4);         \
   } while (0)
   if (R == 32) TS_DS(32);
-  else TS_DS(16);
+  else if (R == 16) TS_DS(16);
+  else TS_DS(8);
 #undef TS_DS
   TS_LAUNCH_CHECK();
 }

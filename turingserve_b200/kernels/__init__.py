@@ -140,6 +140,9 @@ class CudaOps:
         self.lib.ts_attention_diff_mma_supported.restype = c_int
         self.lib.ts_attention_diff_mma_scratch_floats.argtypes = [I, I, I, I]
         self.lib.ts_attention_diff_mma_scratch_floats.restype = ctypes.c_longlong
+        self.lib.ts_set_delta_rows.argtypes = [I]
+        self.lib.ts_set_delta_rows.restype = None
+        self.lib.ts_set_delta_rows(int(os.environ.get("TURINGSERVE_B200_DELTA_ROWS", "0")))
         self.lib.ts_attention_biased_mma_supported.argtypes = [I, I, I, I, I, I]
         self.lib.ts_attention_biased_mma_supported.restype = c_int
         self.lib.ts_attention_biased_mma_chunk.argtypes = [I, I, I]
@@ -763,7 +766,7 @@ class CudaOps:
             ms = 1
             if step.num_decode > 0 and H // KVH <= 64:
                 ms = min(16, splits) if splits > 0 else max(1, min(16, 2 * self.num_sms // max(1, step.num_decode * KVH * chunks),
-                                                                   reach // 256))
+                                                                   reach // 128))
             scratch = counters = None
             if ms > 1:
                 scratch = self._buffer("biased_mma_scratch", self.lib.ts_attention_biased_mma_scratch_floats(B, KVH, Dk, Dv, v_in_k, ms),
