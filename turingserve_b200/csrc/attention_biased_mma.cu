@@ -416,7 +416,7 @@ TS_API int ts_attention_biased_mma(void* out, int out_ts, int out_hs, const void
                                   (const bf16*)v_cache, block_tables, q_start, seq_lens, B, table_width, max_q_len, H, KVH, \
                                   page, scale, softcap, slopes, window, CHUNKS, splits, scratch, counters, s)
   if (inst == 1) TS_BM(64, 64, false, 3, 1);
-  if (inst == 2) TS_BM(128, 128, false, 3, 1);
+  if (inst == 2) TS_BM(128, 128, false, 2, 1);                        // (two stages: 80 KB a block, so two blocks share an SM)
   if (inst == 3) TS_BM(576, 256, true, 2, 2);
   TS_BM(320, 256, true, 3, 1);
 #undef TS_BM
