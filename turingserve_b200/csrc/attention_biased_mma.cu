@@ -13,7 +13,8 @@
 //     a latent row of 512 value columns is two blocks that each redo the scores (128 accumulator registers a thread:
 //     the shared memory of a 576-wide tile allows one block an SM anyway);
 //   * requests that bring ONE token may have their keys cut over `splits` blocks; each leaves (m, l, unnormalised
-//     sum) in scratch and the block that comes last (a ticket counter; nobody waits) merges them in split order.
+//     sum) in scratch and the block that comes last (a ticket counter; nobody waits) merges them in split order; a
+//     second instance of the kernel takes such requests when their rows fill one warp at most (below).
 #include "common.cuh"
 #include "mma_utils.cuh"
 
@@ -23,7 +24,8 @@ constexpr int BM_WARPS = 4;
 constexpr int BM_ROWS = BM_WARPS * 16;
 constexpr int BM_TILE = 64;
 constexpr int BM_PAGES_S = 512;
-constexpr int BM_MAX_SPLITS = 16;
+constexpr int BM_MAX_SPLITS = 16;   // blocks a single-token request's keys are cut over
+constexpr int BM_MAX_RECORDS = 64;  // partial results the last block merges (four a block where the warps share a tile's keys)
 constexpr float BM_LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ float capped(float s, float cap, float inv_cap) {
@@ -31,7 +33,10 @@ __device__ __forceinline__ float capped(float s, float cap, float inv_cap) {
   return cap * (1.f - __fdividef(2.f, t + 1.f));
 }
 
-template <int DK, int DV, bool V_IN_K, int STAGES>
+// SPREAD: for requests that bring ONE token whose rows (the heads of one kv head) fill one warp's 16 at most.  The
+// four warps all take these rows and 16 keys of every tile each (instead of three of them idling) and leave four
+// partial results a block, which the merge folds like those of four blocks.
+template <int DK, int DV, bool V_IN_K, int STAGES, bool SPREAD>
 __global__ void __launch_bounds__(BM_WARPS * 32)
 attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, const bf16* __restrict__ q, int q_ts, int q_hs,
                             const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
@@ -42,6 +47,7 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
   pdl_launch_dependents();
   pdl_wait();
   constexpr int CHK = DK / 8, KS = DK / 16, NT = DV / 8, CHV = DV / 8;
+  constexpr int NTW = SPREAD ? 2 : BM_TILE / 8;                      // groups of 8 keys of a tile this warp takes
   extern __shared__ __align__(128) unsigned char smem[];
   const int b = blockIdx.z, kvh = blockIdx.y;
   const int G = H / KVH;
@@ -56,6 +62,9 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
   const int row0 = (n_row_tiles - 1 - tile) * BM_ROWS;               // longest tiles first
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int prefix = seq_len - q_len;
+  if (SPREAD && (q_len != 1 || n_rows > 16)) return;                 // (the launcher sends only such requests)
+  const int wrow = SPREAD ? 0 : warp * 16;                           // first row of this warp within the tile
+  const int nt0 = SPREAD ? warp * 2 : 0;                             // its first group of 8 keys within a tile
 
   unsigned char* q_s = smem;                                         // [64][DK]
   unsigned char* k_s = q_s + BM_ROWS * DK * 2;                       // [STAGES][64][DK]
@@ -69,7 +78,7 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
   bf16* optr[2];
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
-    const int row = row0 + warp * 16 + (lane >> 2) + 8 * r;
+    const int row = row0 + wrow + (lane >> 2) + 8 * r;
     if (row < n_rows) {
       const int t = row / G, g = row % G;
       pos[r] = prefix + t;
@@ -82,13 +91,12 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
     }
   }
   // the query tile
-  for (int idx = threadIdx.x; idx < BM_ROWS * CHK; idx += BM_WARPS * 32) {
+  // (only the rows that exist: what the others' places in shared memory hold reaches nothing, since every row of a
+  // product depends on its own query row alone and a row without a position is masked whatever its scores are)
+  for (int idx = threadIdx.x; idx < min(BM_ROWS, n_rows - row0) * CHK; idx += BM_WARPS * 32) {
     const int r = idx / CHK, c = idx % CHK;
     const int row = row0 + r;
-    const bool ok = row < n_rows;
-    const bf16* src = q;
-    if (ok) src = q + (size_t)(qs + row / G) * q_ts + (size_t)(kvh * G + row % G) * q_hs + c * 8;
-    cp_async_16(q_s + swz<DK>(r, c), src, ok);
+    cp_async_16(q_s + swz<DK>(r, c), q + (size_t)(qs + row / G) * q_ts + (size_t)(kvh * G + row % G) * q_hs + c * 8, true);
   }
   cp_async_commit();
 
@@ -104,7 +112,7 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
     j_lo = first;
   }
   const int n_tiles = (seq_len > 0 && j_hi >= j_lo) ? (j_hi - j_lo) / BM_TILE + 1 : 0;
-  const int w_first = row0 + warp * 16, w_last = min(w_first + 15, n_rows - 1);
+  const int w_first = row0 + wrow, w_last = min(w_first + 15, n_rows - 1);
   const int w_pos_lo = prefix + w_first / G, w_pos_hi = (w_first < n_rows) ? prefix + w_last / G : -1;
 
   const int page_shift = (page & (page - 1)) == 0 ? 31 - __clz(page) : -1;
@@ -118,12 +126,17 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
   }
   const int v_width = DV * v_chunks;                                 // a value row's width in its own tensor
 
+  // A tile's keys are dealt out to groups of LPK lanes, which bring a key row's 16-byte pieces: the row's place in the
+  // cache is worked out once a key, not once a piece (index arithmetic per piece cost more issue slots than the products).
+  constexpr int LPK = CHK >= 32 ? 32 : (CHK >= 16 ? 16 : 8);         // lanes a key
+  constexpr int KPI = BM_WARPS * (32 / LPK);                         // keys the block brings in one round
   auto load_tile = [&](int t, int stage) {
     const int j0 = j_lo + t * BM_TILE;
     unsigned char* ks_ = k_s + (size_t)stage * BM_TILE * DK * 2;
     unsigned char* vs_ = v_s + (size_t)stage * BM_TILE * DV * 2;
-    for (int idx = threadIdx.x; idx < BM_TILE * (CHK + (V_IN_K ? 0 : CHV)); idx += BM_WARPS * 32) {
-      const int key = idx / (CHK + (V_IN_K ? 0 : CHV)), c = idx % (CHK + (V_IN_K ? 0 : CHV));
+    const int c0 = lane % LPK;
+#pragma unroll 2
+    for (int key = warp * (32 / LPK) + lane / LPK; key < BM_TILE; key += KPI) {
       const int j = j0 + key;
       const bool ok = j <= j_hi;
       size_t tok = 0;
@@ -132,8 +145,14 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
         const int pg = pages_staged ? pages_s[lp - page_first] : block_tables[(size_t)b * table_width + lp];
         tok = ((size_t)pg * KVH + kvh) * page + (size_t)(j - lp * page);
       }
-      if (c < CHK) cp_async_16(ks_ + swz<DK>(key, c), k_cache + tok * DK + c * 8, ok);
-      else cp_async_16(vs_ + swz<DV>(key, c - CHK), v_cache + tok * v_width + chunk * DV + (c - CHK) * 8, ok);
+      const bf16* krow = k_cache + tok * DK;
+#pragma unroll
+      for (int c = c0; c < CHK; c += LPK) cp_async_16(ks_ + swz<DK>(key, c), krow + c * 8, ok);
+      if (!V_IN_K) {
+        const bf16* vrow = v_cache + tok * v_width + chunk * DV;
+#pragma unroll
+        for (int c = c0; c < CHV; c += LPK) cp_async_16(vs_ + swz<DV>(key, c), vrow + c * 8, ok);
+      }
     }
   };
 
@@ -159,17 +178,17 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
     const bool in_future = j0 > w_pos_hi;                                          // warp-uniform
     const bool in_past = window > 0 && (j0 + BM_TILE - 1) < (w_pos_lo - window + 1);
     if (!in_future && !in_past) {
-      float s_acc[BM_TILE / 8][4];
+      float s_acc[NTW][4];
 #pragma unroll
-      for (int nt = 0; nt < BM_TILE / 8; ++nt) s_acc[nt][0] = s_acc[nt][1] = s_acc[nt][2] = s_acc[nt][3] = 0.f;
+      for (int nt = 0; nt < NTW; ++nt) s_acc[nt][0] = s_acc[nt][1] = s_acc[nt][2] = s_acc[nt][3] = 0.f;
 #pragma unroll 4
       for (int ks = 0; ks < KS; ++ks) {
         const int mat = lane >> 3, r = lane & 7;
         unsigned qf[4];
-        ldmatrix_x4(qf[0], qf[1], qf[2], qf[3], q_s + swz<DK>(warp * 16 + (mat & 1) * 8 + r, ks * 2 + (mat >> 1)));
+        ldmatrix_x4(qf[0], qf[1], qf[2], qf[3], q_s + swz<DK>(wrow + (mat & 1) * 8 + r, ks * 2 + (mat >> 1)));
 #pragma unroll
-        for (int np = 0; np < BM_TILE / 16; ++np) {
-          const int key = np * 16 + (mat >> 1) * 8 + r;
+        for (int np = 0; np < NTW / 2; ++np) {
+          const int key = (nt0 / 2 + np) * 16 + (mat >> 1) * 8 + r;
           const int c = ks * 2 + (mat & 1);
           unsigned b0, b1, b2, b3;
           ldmatrix_x4(b0, b1, b2, b3, ks_ + swz<DK>(key, c));
@@ -180,10 +199,10 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
       // scale, cap, bias, mask; online softmax in the exp2 domain
       float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-      for (int nt = 0; nt < BM_TILE / 8; ++nt)
+      for (int nt = 0; nt < NTW; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const int j = j0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+          const int j = j0 + (nt0 + nt) * 8 + (lane & 3) * 2 + (e & 1);
           const int p = pos[e >> 1];
           float v = s_acc[nt][e] * scale;
           if (softcap > 0.f) v = capped(v, softcap, inv_cap);
@@ -205,7 +224,7 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
       }
       float rs[2] = {0.f, 0.f};
 #pragma unroll
-      for (int nt = 0; nt < BM_TILE / 8; ++nt)
+      for (int nt = 0; nt < NTW; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float p = exp2f(s_acc[nt][e] - m_use[e >> 1]);
@@ -227,7 +246,7 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
       }
       // O += P . V, 16 keys at a time; P as two bfloat16 terms
 #pragma unroll
-      for (int kk = 0; kk < BM_TILE / 16; ++kk) {
+      for (int kk = 0; kk < NTW / 2; ++kk) {
         unsigned hi[4], lo[4];
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
@@ -239,7 +258,7 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
 #pragma unroll
         for (int i = 0; i < NT; i += 2) {
           const int mat = lane >> 3, r = lane & 7;
-          const int key = kk * 16 + (mat & 1) * 8 + r;
+          const int key = (nt0 / 2 + kk) * 16 + (mat & 1) * 8 + r;
           const int c = i + (mat >> 1);
           unsigned b0, b1, b2, b3;
           if (V_IN_K) ldmatrix_x4_trans(b0, b1, b2, b3, vs_ + swz<DK>(key, chunk * CHV + c));
@@ -255,7 +274,7 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
   }
   cp_async_wait<0>();
 
-  if (my_splits == 1) {
+  if (!SPREAD && my_splits == 1) {
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       if (optr[r] == nullptr) continue;
@@ -269,15 +288,16 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
     return;
   }
 
-  // partial results of a single-token request: [request][kv head][chunk][split][row][DV + 2] (one row tile: G <= 64)
-  constexpr int REC = DV + 2;
+  // partial results of a single-token request: [request][kv head][chunk][split][row][DV + 4] (one row tile: G <= 64)
+  constexpr int REC = DV + 4;                                        // m, l, two floats of padding, the sums (16-byte rows)
   const size_t group = ((size_t)(b * KVH + kvh) * v_chunks + chunk) * splits;
   float* mine = scratch + (group + split) * BM_ROWS * REC;
+  // (a block's 64 records: its rows, or, where the warps shared the keys, 16 rows of each of the four warps)
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
-    const int row = warp * 16 + (lane >> 2) + 8 * r;
+    const int row = wrow + (lane >> 2) + 8 * r;
     if (row >= n_rows) continue;
-    float* dst = mine + (size_t)row * REC;
+    float* dst = mine + (size_t)(SPREAD ? warp * 16 + row : row) * REC;
     if ((lane & 3) == 0) {
       dst[0] = m_run[r];
       dst[1] = l_run[r];
@@ -285,8 +305,7 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
 #pragma unroll
     for (int i = 0; i < NT; ++i) {
       const int d = i * 8 + (lane & 3) * 2;
-      dst[2 + d] = o[i][2 * r];
-      dst[3 + d] = o[i][2 * r + 1];
+      *reinterpret_cast<float2*>(dst + 4 + d) = make_float2(o[i][2 * r], o[i][2 * r + 1]);
     }
   }
   __threadfence();
@@ -303,49 +322,59 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
   // The merge, by the block that came last.  Every load of another block's numbers is independent of the others and
   // issued before any is used: a chain of dependent L2 round trips, one a split, would cost more than the attention.
   const float* all = scratch + group * BM_ROWS * REC;
-  float* m_m = reinterpret_cast<float*>(smem);                       // [64][16] maxima, then weights (the tiles are done with)
-  float* l_m = m_m + BM_ROWS * BM_MAX_SPLITS;                        // [64][16] sums
-  for (int idx = threadIdx.x; idx < n_rows * my_splits; idx += BM_WARPS * 32) {
-    const int row = idx / my_splits, sp = idx % my_splits;
-    const float2 ml = __ldcg(reinterpret_cast<const float2*>(all + ((size_t)sp * BM_ROWS + row) * REC));
-    m_m[row * BM_MAX_SPLITS + sp] = ml.x;
-    l_m[row * BM_MAX_SPLITS + sp] = ml.y;
+  constexpr int PER_BLOCK = SPREAD ? 4 : 1;
+  const int n_rec = my_splits * PER_BLOCK;
+  // record k of row `row`: block k / PER_BLOCK, and within it the warp k % PER_BLOCK where the warps shared the keys
+  auto rec_of = [&](int k, int row) {
+    return all + ((size_t)(k / PER_BLOCK) * BM_ROWS + (SPREAD ? (k % PER_BLOCK) * 16 : 0) + row) * REC;
+  };
+  float* m_m = reinterpret_cast<float*>(smem);                       // [64][64] maxima, then weights (the tiles are done with)
+  float* l_m = m_m + BM_ROWS * BM_MAX_RECORDS;                       // [64][64] sums
+  for (int idx = threadIdx.x; idx < n_rows * n_rec; idx += BM_WARPS * 32) {
+    const int row = idx / n_rec, k = idx % n_rec;
+    const float2 ml = __ldcg(reinterpret_cast<const float2*>(rec_of(k, row)));
+    m_m[row * BM_MAX_RECORDS + k] = ml.x;
+    l_m[row * BM_MAX_RECORDS + k] = ml.y;
   }
   __syncthreads();
   for (int row = threadIdx.x; row < n_rows; row += BM_WARPS * 32) {
     float mm = -INFINITY;
-    for (int sp = 0; sp < my_splits; ++sp) mm = fmaxf(mm, m_m[row * BM_MAX_SPLITS + sp]);
+    for (int k = 0; k < n_rec; ++k) mm = fmaxf(mm, m_m[row * BM_MAX_RECORDS + k]);
     float ll = 0.f;
-    for (int sp = 0; sp < my_splits; ++sp) {
-      const float pm = m_m[row * BM_MAX_SPLITS + sp];
+    for (int k = 0; k < n_rec; ++k) {
+      const float pm = m_m[row * BM_MAX_RECORDS + k];
       const float w = pm == -INFINITY ? 0.f : exp2f(pm - mm);
-      m_m[row * BM_MAX_SPLITS + sp] = w;
-      ll = fmaf(l_m[row * BM_MAX_SPLITS + sp], w, ll);
+      m_m[row * BM_MAX_RECORDS + k] = w;
+      ll = fmaf(l_m[row * BM_MAX_RECORDS + k], w, ll);
     }
     const float inv = ll > 0.f ? 1.f / ll : 0.f;
-    for (int sp = 0; sp < my_splits; ++sp) m_m[row * BM_MAX_SPLITS + sp] *= inv;
+    for (int k = 0; k < n_rec; ++k) m_m[row * BM_MAX_RECORDS + k] *= inv;
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < n_rows * (DV / 2); idx += BM_WARPS * 32) {
-    const int row = idx / (DV / 2), d = (idx % (DV / 2)) * 2;
-    float2 v[BM_MAX_SPLITS];
+  for (int idx = threadIdx.x; idx < n_rows * (DV / 4); idx += BM_WARPS * 32) {
+    const int row = idx / (DV / 4), d = (idx % (DV / 4)) * 4;
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+    for (int k0 = 0; k0 < n_rec; k0 += 16) {                         // sixteen loads in flight, then their sum, in record order
+      float4 v[16];
 #pragma unroll
-    for (int sp = 0; sp < BM_MAX_SPLITS; ++sp)
-      v[sp] = sp < my_splits ? __ldcg(reinterpret_cast<const float2*>(all + ((size_t)sp * BM_ROWS + row) * REC + 2 + d))
-                             : make_float2(0.f, 0.f);
-    float a0 = 0.f, a1 = 0.f;
+      for (int u = 0; u < 16; ++u)
+        v[u] = k0 + u < n_rec ? __ldcg(reinterpret_cast<const float4*>(rec_of(k0 + u, row) + 4 + d)) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for (int sp = 0; sp < BM_MAX_SPLITS; ++sp) {
-      const float w = sp < my_splits ? m_m[row * BM_MAX_SPLITS + sp] : 0.f;
-      a0 = fmaf(v[sp].x, w, a0);
-      a1 = fmaf(v[sp].y, w, a1);
+      for (int u = 0; u < 16; ++u) {
+        const float w = k0 + u < n_rec ? m_m[row * BM_MAX_RECORDS + k0 + u] : 0.f;
+        a0 = fmaf(v[u].x, w, a0);
+        a1 = fmaf(v[u].y, w, a1);
+        a2 = fmaf(v[u].z, w, a2);
+        a3 = fmaf(v[u].w, w, a3);
+      }
     }
     bf16* dst = out + (size_t)qs * out_ts + (size_t)(kvh * G + row) * out_hs + chunk * DV + d;
     *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(a0, a1);
+    *reinterpret_cast<__nv_bfloat162*>(dst + 2) = __floats2bfloat162_rn(a2, a3);
   }
 }
 
-template <int DK, int DV, bool V_IN_K, int STAGES>
+template <int DK, int DV, bool V_IN_K, int STAGES, bool SPREAD>
 int launch(bf16* out, int out_ts, int out_hs, const bf16* q, int q_ts, int q_hs, const bf16* k_cache, const bf16* v_cache,
            const int* block_tables, const int* q_start, const int* seq_lens, int B, int table_width, int max_q_len, int H,
            int KVH, int page, float scale, float softcap, const float* slopes, int window, int v_chunks, int splits,
@@ -353,14 +382,14 @@ int launch(bf16* out, int out_ts, int out_hs, const bf16* q, int q_ts, int q_hs,
   const size_t smem = (size_t)BM_ROWS * DK * 2 + (size_t)STAGES * BM_TILE * DK * 2 + (V_IN_K ? 0 : (size_t)STAGES * BM_TILE * DV * 2);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_biased_mma_kernel<DK, DV, V_IN_K, STAGES>,
+    cudaError_t e = cudaFuncSetAttribute(attention_biased_mma_kernel<DK, DV, V_IN_K, STAGES, SPREAD>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) TS_REFUSE((int)e, "ts_attention_biased_mma: shared memory %zu: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
   const int G = H / KVH;
   dim3 grid(ceil_div(max_q_len * G, BM_ROWS) * v_chunks * splits, KVH, B);
-  ts_launch(attention_biased_mma_kernel<DK, DV, V_IN_K, STAGES>, dim3(grid), dim3(BM_WARPS * 32), smem, s, out, out_ts, out_hs, q,
+  ts_launch(attention_biased_mma_kernel<DK, DV, V_IN_K, STAGES, SPREAD>, dim3(grid), dim3(BM_WARPS * 32), smem, s, out, out_ts, out_hs, q,
             q_ts, q_hs, k_cache, v_cache, block_tables, q_start, seq_lens, table_width, H, KVH, page, scale, softcap, slopes,
             window, v_chunks, splits, scratch, counters);
   TS_LAUNCH_CHECK();
@@ -389,17 +418,19 @@ TS_API int ts_attention_biased_mma_chunk(int Dk, int Dv, int v_in_k) {
 
 TS_API long long ts_attention_biased_mma_scratch_floats(int B, int KVH, int Dk, int Dv, int v_in_k, int splits) {
   const int chunk = ts_attention_biased_mma_chunk(Dk, Dv, v_in_k);
-  if (splits <= 1 || chunk == 0) return 0;
-  return (long long)B * KVH * (Dv / chunk) * splits * BM_ROWS * (chunk + 2);
+  if (chunk == 0) return 0;
+  return (long long)B * KVH * (Dv / chunk) * (splits < 1 ? 1 : splits) * BM_ROWS * (chunk + 4);
 }
 
 // As ts_attention_biased; bfloat16 only; q rows 16-byte aligned (strides multiples of 8).  splits > 1 (at most 16,
 // and only where a kv head serves at most 64 heads) needs scratch and zeroed counters, one per (request, kv head, chunk).
+// spread: every request of the launch brings one token of at most 16 rows; the instance whose warps share each tile's
+// keys runs (scratch and counters are needed at every split count).
 TS_API int ts_attention_biased_mma(void* out, int out_ts, int out_hs, const void* q, int q_ts, int q_hs, const void* k_cache,
                                    const void* v_cache, const int* block_tables, const int* q_start, const int* seq_lens,
                                    int B, int table_width, int max_q_len, int H, int KVH, int Dk, int Dv, int page,
                                    float scale, float softcap, const float* slopes, int window, int splits, float* scratch,
-                                   int* counters, void* stream) {
+                                   int* counters, int spread, void* stream) {
   if (B <= 0 || max_q_len <= 0) return 0;
   const int v_in_k = v_cache == nullptr;
   const int inst = (KVH > 0 && H % KVH == 0) ? instance_of(Dk, Dv, v_in_k) : 0;
@@ -410,11 +441,19 @@ TS_API int ts_attention_biased_mma(void* out, int out_ts, int out_hs, const void
   if (splits < 1) splits = 1;
   if (splits > 1 && (splits > BM_MAX_SPLITS || H / KVH > BM_ROWS || scratch == nullptr || counters == nullptr))
     TS_REFUSE(TS_ERR_LIMIT, "ts_attention_biased_mma: %d splits", splits);
+  if (spread && (max_q_len != 1 || H / KVH > 16 || scratch == nullptr || counters == nullptr))
+    TS_REFUSE(TS_ERR_SHAPE, "ts_attention_biased_mma: the warps share the keys of single tokens with at most 16 rows, through scratch");
   cudaStream_t s = (cudaStream_t)stream;
-#define TS_BM(DKK, DVV, VK, ST, CHUNKS)                                                                                   \
-  return launch<DKK, DVV, VK, ST>((bf16*)out, out_ts, out_hs, (const bf16*)q, q_ts, q_hs, (const bf16*)k_cache,             \
-                                  (const bf16*)v_cache, block_tables, q_start, seq_lens, B, table_width, max_q_len, H, KVH, \
-                                  page, scale, softcap, slopes, window, CHUNKS, splits, scratch, counters, s)
+#define TS_BM(DKK, DVV, VK, ST, CHUNKS)                                                                                       \
+  do {                                                                                                                        \
+    if (spread)                                                                                                               \
+      return launch<DKK, DVV, VK, ST, true>((bf16*)out, out_ts, out_hs, (const bf16*)q, q_ts, q_hs, (const bf16*)k_cache,     \
+                                            (const bf16*)v_cache, block_tables, q_start, seq_lens, B, table_width, max_q_len, \
+                                            H, KVH, page, scale, softcap, slopes, window, CHUNKS, splits, scratch, counters, s); \
+    return launch<DKK, DVV, VK, ST, false>((bf16*)out, out_ts, out_hs, (const bf16*)q, q_ts, q_hs, (const bf16*)k_cache,      \
+                                           (const bf16*)v_cache, block_tables, q_start, seq_lens, B, table_width, max_q_len,  \
+                                           H, KVH, page, scale, softcap, slopes, window, CHUNKS, splits, scratch, counters, s); \
+  } while (0)
   if (inst == 1) TS_BM(64, 64, false, 3, 1);
   if (inst == 2) TS_BM(128, 128, false, 2, 1);                        // (two stages: 80 KB a block, so two blocks share an SM)
   if (inst == 3) TS_BM(576, 256, true, 2, 2);

@@ -125,7 +125,7 @@ class CudaOps:
             "ts_delta_scan": [P, P, P, I, P, ctypes.c_longlong, P, P, I, I, I, I, I, I, I, P],
             "ts_head_gated_rmsnorm": [P, P, P, I, P, F, I, I, I, I, P],
             "ts_attention_biased": [P, I, I, P, I, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, P, I, I, P, P, I, P],
-            "ts_attention_biased_mma": [P, I, I, P, I, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, P, I, I, P, P, P],
+            "ts_attention_biased_mma": [P, I, I, P, I, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, P, I, I, P, P, I, P],
             "ts_rms_rows": [P, P, I, I, I, P, F, I, I, P],
             "ts_qk_rownorm_write": [P, I, P, P, F, P, F, I, P, P, P, I, I, I, I, I, I, P],
             "ts_latent_kv_write": [P, I, I, P, F, P, P, F, I, P, P, I, I, I, I, I, P],
@@ -763,20 +763,38 @@ class CudaOps:
                 and self.lib.ts_attention_biased_mma_supported(H, KVH, Dk, Dv, v_in_k, _code(q.dtype))):
             # the tensor-core kernel: key rows of 64, 128 (values of the same width) or latent rows with the values inside
             chunks = Dv // self.lib.ts_attention_biased_mma_chunk(Dk, Dv, v_in_k)
+            nd, G = step.num_decode, H // KVH
+            width = block_tables.shape[1]
+            # Requests that bring one token: their keys cut over blocks.  Where a kv head serves at most 16 heads they go
+            # to the instance whose four warps share every tile's keys (a launch of their own, four partial results a
+            # block); else they ride in the other requests' launch, one warp a block at work on them.
+            spread = nd > 0 and G <= 16
             ms = 1
-            if step.num_decode > 0 and H // KVH <= 64:
-                ms = min(16, splits) if splits > 0 else max(1, min(16, 2 * self.num_sms // max(1, step.num_decode * KVH * chunks),
-                                                                   reach // 128))
-            scratch = counters = None
-            if ms > 1:
-                scratch = self._buffer("biased_mma_scratch", self.lib.ts_attention_biased_mma_scratch_floats(B, KVH, Dk, Dv, v_in_k, ms),
-                                       torch.float32, q.device, floor=1 << 20)
-                counters = self._buffer("biased_mma_counters", B * KVH * chunks, torch.int32, q.device, floor=1 << 14, zero=True)
-            rc = self.lib.ts_attention_biased_mma(
-                _ptr(out), out.stride(0), out.stride(1), _ptr(q), q.stride(0), q.stride(1), _ptr(k_cache), _ptr(v_cache),
-                _ptr(block_tables), _ptr(step.q_start), _ptr(step.seq_lens), B, block_tables.shape[1], step.max_q_len, H, KVH,
-                Dk, Dv, page_size, float(scale), float(softcap), _ptr(slopes), w, ms, _ptr(scratch), _ptr(counters),
-                self._stream())
+            if nd > 0 and G <= 64:
+                ms = max(1, min(16, (8 if spread else 16) if splits <= 0 else splits,
+                                2 * self.num_sms // max(1, nd * KVH * chunks), reach // (256 if spread else 128)))
+
+            def launch(first: int, count: int, max_q: int, n_splits: int, spread_flag: int) -> int:
+                scratch = counters = None
+                if n_splits > 1 or spread_flag:
+                    scratch = self._buffer("biased_mma_scratch",
+                                           self.lib.ts_attention_biased_mma_scratch_floats(count, KVH, Dk, Dv, v_in_k, n_splits),
+                                           torch.float32, q.device, floor=1 << 20)
+                    counters = self._buffer("biased_mma_counters", count * KVH * chunks, torch.int32, q.device, floor=1 << 14,
+                                            zero=True)
+                return self.lib.ts_attention_biased_mma(
+                    _ptr(out), out.stride(0), out.stride(1), _ptr(q), q.stride(0), q.stride(1), _ptr(k_cache), _ptr(v_cache),
+                    block_tables.data_ptr() + 4 * first * width, step.q_start.data_ptr() + 4 * first,
+                    step.seq_lens.data_ptr() + 4 * first, count, width, max_q, H, KVH, Dk, Dv, page_size, float(scale),
+                    float(softcap), _ptr(slopes), w, n_splits, _ptr(scratch), _ptr(counters), spread_flag, self._stream())
+
+            if spread:
+                rc = launch(0, nd, 1, ms, 1)
+                if rc == 0 and nd < B:
+                    self.launches += 1
+                    rc = launch(nd, B - nd, step.max_q_len, 1, 0)
+            else:
+                rc = launch(0, B, step.max_q_len, ms, 0)
             if rc != self.UNSUPPORTED:
                 self._check(rc, "attention_biased_mma")
                 return
