@@ -740,13 +740,13 @@ def pizunex_config(z: dict, groups: int, vocab: int):
     """``groups`` times four layers: (attention, dense), (latent attention, dense), (delta rule, none), (delta rule, dense)."""
     from turingserve_b200.models.pizunex import make_config
     att = {"type": "attention", "mixer": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
-                                          "scale": z["dim"] ** -0.5, "softcap": 50.0, "mask": {"size": z["window"]},
-                                          "q_temp": {"coef": 0.3, "every": 64}}}
+                                          "scale": z["dim"] ** -0.5, "softcap": 30.0, "mask": {"size": z["window"]},
+                                          "q_temp": {"coef": 0.1, "every": 128}}}
     lat = {"type": "latent_attention",
            "mixer": {"heads": z["lheads"], "dim": z["nope"], "rot_dim": z["rope"], "vdim": z["lvdim"], "q_rank": z["q_rank"],
                      "kv_rank": z["kv_rank"], "scale": (z["nope"] + z["rope"]) ** -0.5,
                      "rot": {"base": 10000.0, "dims": z["rope"],
-                             "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+                             "scaling": {"factor": 8.0, "original": 4096, "fast": 16.0, "slow": 2.0}}}}
     dlt = {"type": "delta", "mixer": {"heads": z["dheads"], "kv_heads": z["dkv"], "dim": z["ddim"], "vdim": z["dvdim"], "conv": 4}}
     dense = {"kind": "dense", "ff": z["ff"]}
     four = [{**att, "mlp": dense}, {**lat, "mlp": dense}, {**dlt, "mlp": None}, {**dlt, "mlp": dense}]
@@ -809,7 +809,7 @@ def pizunex_kernels(ops, z: dict, pk: dict, T: int, B: int, ctx: int, page: int)
         step = SimpleNamespace(q_start=i32([i * per for i in range(reqs + 1)]), seq_lens=i32([seq] * reqs), num_requests=reqs,
                                num_decode=reqs if per == 1 else 0, max_q_len=per, max_seq_len=seq)
         bt = tables_for(reqs, seq, width)
-        ms = timed(lambda: ops.attention_biased(o, q, kc, vc, bt, step, G, page, D ** -0.5, 50.0, slopes, win), flush)
+        ms = timed(lambda: ops.attention_biased(o, q, kc, vc, bt, step, G, page, D ** -0.5, 30.0, slopes, win), flush)
         seen = sum(min(i + 1, win) for i in range(seq - per, seq))       # keys a request's queries see
         flops = 4.0 * D * H * seen * reqs
         byts = reqs * min(seq, win + per) * G * 2 * D * 2.0
