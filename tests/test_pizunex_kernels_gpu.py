@@ -279,12 +279,14 @@ def plain_attention(q, k, v, KVH, scale, cap, slopes, window, first_pos):
     (4, 2, 16, 16, 8, 9, 6.0, False), (6, 6, 8, 8, 4, 33, None, False), (2, 1, 40, 40, 16, 3, 20.0, False),
     (4, 1, 28, 20, 16, None, None, True), (3, 1, 80, 64, 64, None, None, True), (4, 2, 64, 64, 64, 70, 30.0, False),
     (20, 1, 30, 30, 8, None, 4.0, False), (6, 2, 128, 128, 16, 48, 25.0, False), (5, 1, 576, 512, 64, None, None, True),
-    (3, 1, 320, 256, 16, None, None, True), (4, 4, 64, 64, 8, None, None, False)])
+    (3, 1, 320, 256, 16, None, None, True), (4, 4, 64, 64, 8, None, None, False), (20, 1, 64, 64, 8, None, 4.0, False),
+    (24, 1, 320, 256, 16, None, None, True), (40, 1, 128, 128, 16, 25, None, False)])
 def test_biased_attention_in_batches_of_unequal_requests(ops, dtype, H, KVH, Dk, Dv, page, window, cap, shared):
     """A prompt from position 0, a portion in the middle of a context, two single tokens (one with a context of one
     key), in one launch, pages in a shuffled pool; against each request alone in the plain functions.  ``shared``:
     no value tensor, the values are the first Dv columns of the key rows.  In bfloat16 the widths 64, 128, 320 and 576
-    go to the tensor-core kernel (values in chunks of 128 columns, keys of single tokens cut over blocks)."""
+    go to the tensor-core kernel (values in chunks of 256 columns, keys of single tokens cut over blocks; up to 16 heads a
+    kv head, up to 32 and more than 32: the three instances for single tokens)."""
     g = torch.Generator(device=DEV).manual_seed(H * Dk)
     q_lens, seq_lens = [1, 1, 21, 13], [1, 77, 21, 90]
     slopes = plain.slopes(H).to(DEV) if not shared else None

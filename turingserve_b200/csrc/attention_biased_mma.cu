@@ -14,7 +14,7 @@
 //     the shared memory of a 576-wide tile allows one block an SM anyway);
 //   * requests that bring ONE token may have their keys cut over `splits` blocks; each leaves (m, l, unnormalised
 //     sum) in scratch and the block that comes last (a ticket counter; nobody waits) merges them in split order; a
-//     second instance of the kernel takes such requests when their rows fill one warp at most (below).
+//     second and a third instance of the kernel take such requests when their rows fill one or two warps (below).
 #include "common.cuh"
 #include "mma_utils.cuh"
 
@@ -33,10 +33,10 @@ __device__ __forceinline__ float capped(float s, float cap, float inv_cap) {
   return cap * (1.f - __fdividef(2.f, t + 1.f));
 }
 
-// SPREAD: for requests that bring ONE token whose rows (the heads of one kv head) fill one warp's 16 at most.  The
-// four warps all take these rows and 16 keys of every tile each (instead of three of them idling) and leave four
-// partial results a block, which the merge folds like those of four blocks.
-template <int DK, int DV, bool V_IN_K, int STAGES, bool SPREAD>
+// SPREAD (1 or 2; 0: off): for requests that bring ONE token whose rows (the heads of one kv head) fill SPREAD warps'
+// 16 rows at most.  The 4 / SPREAD warps of a row group all take its rows and 64 / (4 / SPREAD) keys of every tile
+// each (instead of idling) and leave as many partial results a block, which the merge folds like those of blocks.
+template <int DK, int DV, bool V_IN_K, int STAGES, int SPREAD>
 __global__ void __launch_bounds__(BM_WARPS * 32)
 attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, const bf16* __restrict__ q, int q_ts, int q_hs,
                             const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
@@ -47,7 +47,8 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
   pdl_launch_dependents();
   pdl_wait();
   constexpr int CHK = DK / 8, KS = DK / 16, NT = DV / 8, CHV = DV / 8;
-  constexpr int NTW = SPREAD ? 2 : BM_TILE / 8;                      // groups of 8 keys of a tile this warp takes
+  constexpr int WPG = SPREAD ? BM_WARPS / SPREAD : 1;                // warps that share a row group's keys
+  constexpr int NTW = BM_TILE / 8 / WPG;                             // groups of 8 keys of a tile this warp takes
   extern __shared__ __align__(128) unsigned char smem[];
   const int b = blockIdx.z, kvh = blockIdx.y;
   const int G = H / KVH;
@@ -62,9 +63,9 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
   const int row0 = (n_row_tiles - 1 - tile) * BM_ROWS;               // longest tiles first
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int prefix = seq_len - q_len;
-  if (SPREAD && (q_len != 1 || n_rows > 16)) return;                 // (the launcher sends only such requests)
-  const int wrow = SPREAD ? 0 : warp * 16;                           // first row of this warp within the tile
-  const int nt0 = SPREAD ? warp * 2 : 0;                             // its first group of 8 keys within a tile
+  if (SPREAD && (q_len != 1 || n_rows > 16 * SPREAD)) return;        // (the launcher sends only such requests)
+  const int wrow = SPREAD ? (warp / WPG) * 16 : warp * 16;           // first row of this warp within the tile
+  const int nt0 = SPREAD ? (warp % WPG) * NTW : 0;                   // its first group of 8 keys within a tile
 
   unsigned char* q_s = smem;                                         // [64][DK]
   unsigned char* k_s = q_s + BM_ROWS * DK * 2;                       // [STAGES][64][DK]
@@ -292,12 +293,12 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
   constexpr int REC = DV + 4;                                        // m, l, two floats of padding, the sums (16-byte rows)
   const size_t group = ((size_t)(b * KVH + kvh) * v_chunks + chunk) * splits;
   float* mine = scratch + (group + split) * BM_ROWS * REC;
-  // (a block's 64 records: its rows, or, where the warps shared the keys, 16 rows of each of the four warps)
+  // (a block's 64 records: its rows, or, where warps shared the keys, 16 rows of each of the four warps)
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     const int row = wrow + (lane >> 2) + 8 * r;
     if (row >= n_rows) continue;
-    float* dst = mine + (size_t)(SPREAD ? warp * 16 + row : row) * REC;
+    float* dst = mine + (size_t)(SPREAD ? warp * 16 + row % 16 : row) * REC;
     if ((lane & 3) == 0) {
       dst[0] = m_run[r];
       dst[1] = l_run[r];
@@ -322,11 +323,11 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
   // The merge, by the block that came last.  Every load of another block's numbers is independent of the others and
   // issued before any is used: a chain of dependent L2 round trips, one a split, would cost more than the attention.
   const float* all = scratch + group * BM_ROWS * REC;
-  constexpr int PER_BLOCK = SPREAD ? 4 : 1;
-  const int n_rec = my_splits * PER_BLOCK;
-  // record k of row `row`: block k / PER_BLOCK, and within it the warp k % PER_BLOCK where the warps shared the keys
+  const int n_rec = my_splits * WPG;
+  // record k of row `row`: block k / WPG, and within it, where warps shared the keys, warp k % WPG of the row's group
   auto rec_of = [&](int k, int row) {
-    return all + ((size_t)(k / PER_BLOCK) * BM_ROWS + (SPREAD ? (k % PER_BLOCK) * 16 : 0) + row) * REC;
+    const int in_block = SPREAD ? ((row / 16) * WPG + k % WPG) * 16 + row % 16 : row;
+    return all + ((size_t)(k / WPG) * BM_ROWS + in_block) * REC;
   };
   float* m_m = reinterpret_cast<float*>(smem);                       // [64][64] maxima, then weights (the tiles are done with)
   float* l_m = m_m + BM_ROWS * BM_MAX_RECORDS;                       // [64][64] sums
@@ -374,7 +375,7 @@ attention_biased_mma_kernel(bf16* __restrict__ out, int out_ts, int out_hs, cons
   }
 }
 
-template <int DK, int DV, bool V_IN_K, int STAGES, bool SPREAD>
+template <int DK, int DV, bool V_IN_K, int STAGES, int SPREAD>
 int launch(bf16* out, int out_ts, int out_hs, const bf16* q, int q_ts, int q_hs, const bf16* k_cache, const bf16* v_cache,
            const int* block_tables, const int* q_start, const int* seq_lens, int B, int table_width, int max_q_len, int H,
            int KVH, int page, float scale, float softcap, const float* slopes, int window, int v_chunks, int splits,
@@ -424,7 +425,7 @@ TS_API long long ts_attention_biased_mma_scratch_floats(int B, int KVH, int Dk, 
 
 // As ts_attention_biased; bfloat16 only; q rows 16-byte aligned (strides multiples of 8).  splits > 1 (at most 16,
 // and only where a kv head serves at most 64 heads) needs scratch and zeroed counters, one per (request, kv head, chunk).
-// spread: every request of the launch brings one token of at most 16 rows; the instance whose warps share each tile's
+// spread: every request of the launch brings one token of at most 32 rows; an instance whose warps share each tile's
 // keys runs (scratch and counters are needed at every split count).
 TS_API int ts_attention_biased_mma(void* out, int out_ts, int out_hs, const void* q, int q_ts, int q_hs, const void* k_cache,
                                    const void* v_cache, const int* block_tables, const int* q_start, const int* seq_lens,
@@ -441,16 +442,21 @@ TS_API int ts_attention_biased_mma(void* out, int out_ts, int out_hs, const void
   if (splits < 1) splits = 1;
   if (splits > 1 && (splits > BM_MAX_SPLITS || H / KVH > BM_ROWS || scratch == nullptr || counters == nullptr))
     TS_REFUSE(TS_ERR_LIMIT, "ts_attention_biased_mma: %d splits", splits);
-  if (spread && (max_q_len != 1 || H / KVH > 16 || scratch == nullptr || counters == nullptr))
-    TS_REFUSE(TS_ERR_SHAPE, "ts_attention_biased_mma: the warps share the keys of single tokens with at most 16 rows, through scratch");
+  if (spread && (max_q_len != 1 || H / KVH > 32 || scratch == nullptr || counters == nullptr))
+    TS_REFUSE(TS_ERR_SHAPE, "ts_attention_biased_mma: the warps share the keys of single tokens with at most 32 rows, through scratch");
+  const int groups = H / KVH > 16 ? 2 : 1;                            // row groups of 16 among a request's rows
   cudaStream_t s = (cudaStream_t)stream;
 #define TS_BM(DKK, DVV, VK, ST, CHUNKS)                                                                                       \
   do {                                                                                                                        \
+    if (spread && groups == 1)                                                                                                \
+      return launch<DKK, DVV, VK, ST, 1>((bf16*)out, out_ts, out_hs, (const bf16*)q, q_ts, q_hs, (const bf16*)k_cache,        \
+                                         (const bf16*)v_cache, block_tables, q_start, seq_lens, B, table_width, max_q_len,    \
+                                         H, KVH, page, scale, softcap, slopes, window, CHUNKS, splits, scratch, counters, s); \
     if (spread)                                                                                                               \
-      return launch<DKK, DVV, VK, ST, true>((bf16*)out, out_ts, out_hs, (const bf16*)q, q_ts, q_hs, (const bf16*)k_cache,     \
-                                            (const bf16*)v_cache, block_tables, q_start, seq_lens, B, table_width, max_q_len, \
-                                            H, KVH, page, scale, softcap, slopes, window, CHUNKS, splits, scratch, counters, s); \
-    return launch<DKK, DVV, VK, ST, false>((bf16*)out, out_ts, out_hs, (const bf16*)q, q_ts, q_hs, (const bf16*)k_cache,      \
+      return launch<DKK, DVV, VK, ST, 2>((bf16*)out, out_ts, out_hs, (const bf16*)q, q_ts, q_hs, (const bf16*)k_cache,        \
+                                         (const bf16*)v_cache, block_tables, q_start, seq_lens, B, table_width, max_q_len,    \
+                                         H, KVH, page, scale, softcap, slopes, window, CHUNKS, splits, scratch, counters, s); \
+    return launch<DKK, DVV, VK, ST, 0>((bf16*)out, out_ts, out_hs, (const bf16*)q, q_ts, q_hs, (const bf16*)k_cache,      \
                                            (const bf16*)v_cache, block_tables, q_start, seq_lens, B, table_width, max_q_len,  \
                                            H, KVH, page, scale, softcap, slopes, window, CHUNKS, splits, scratch, counters, s); \
   } while (0)

@@ -765,10 +765,10 @@ class CudaOps:
             chunks = Dv // self.lib.ts_attention_biased_mma_chunk(Dk, Dv, v_in_k)
             nd, G = step.num_decode, H // KVH
             width = block_tables.shape[1]
-            # Requests that bring one token: their keys cut over blocks.  Where a kv head serves at most 16 heads they go
-            # to the instance whose four warps share every tile's keys (a launch of their own, four partial results a
-            # block); else they ride in the other requests' launch, one warp a block at work on them.
-            spread = nd > 0 and G <= 16
+            # Requests that bring one token: their keys cut over blocks.  Where a kv head serves at most 32 heads they go
+            # to an instance whose warps share every tile's keys (a launch of their own, four or two partial results a
+            # block); else they ride in the other requests' launch, with the warps that have no rows idle.
+            spread = nd > 0 and G <= 32
             ms = 1
             if nd > 0 and G <= 64:
                 ms = max(1, min(16, (8 if spread else 16) if splits <= 0 else splits,
