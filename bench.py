@@ -778,7 +778,7 @@ def pizunex_kernels(ops, z: dict, pk: dict, T: int, B: int, ctx: int, page: int)
         ready = torch.empty(rows, C + 2 * H + G, device=dev)
         o = torch.empty(rows, H * V, device=dev)
         step = SimpleNamespace(q_start=i32([i * per for i in range(reqs + 1)]), state_slots=i32(list(range(reqs))),
-                               num_requests=reqs, token_request=i32([r for r in range(reqs) for _ in range(per)]))
+                               num_requests=reqs, token_request=i32([r for r in range(reqs) for _ in range(per)]), max_q_len=per)
         ms_p = timed(lambda: ops.delta_prepare(ready, proj, conv_w, a_log, dt, state, step, H, G, D, V, taps, 1e-6), flush)
         ms = timed(lambda: ops.delta_scan(o, ready, proj, state, step, H, G, D, V, taps), flush)
         flops = 8.0 * rows * H * D * V                       # two sums, the decay and the write, 2 operations each

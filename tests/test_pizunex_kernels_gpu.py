@@ -36,7 +36,7 @@ def i32(x):
 def delta_step(n_req, c, slots):
     req = [r for r in range(n_req) for _ in range(c)]
     return SimpleNamespace(q_start=i32([i * c for i in range(n_req + 1)]), state_slots=i32(slots), num_requests=n_req,
-                           token_request=i32(req))
+                           token_request=i32(req), max_q_len=c)
 
 
 def run_delta(ops, proj, conv_w, a_log, dt, state, cuts, slots, H, G, D, V, taps):

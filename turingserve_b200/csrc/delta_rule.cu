@@ -99,7 +99,7 @@ __global__ void __launch_bounds__(256, 1)
 delta_scan_kernel(float* __restrict__ out, const float* __restrict__ ready, const void* __restrict__ proj,
                   int proj_stride, int proj_is_bf16, float* __restrict__ state, size_t state_stride,
                   const int* __restrict__ q_start, const int* __restrict__ slots, int H, int G, int D, int V,
-                  int taps, int P, int vec4) {
+                  int taps, int P, int vec4, int group) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) float smem[];
@@ -126,14 +126,14 @@ delta_scan_kernel(float* __restrict__ out, const float* __restrict__ ready, cons
     const int d = p * R + i;
     s[i] = (live && d < D) ? S[(size_t)d * V + j] : 0.f;
   }
-  for (int i = threadIdx.x; i < DR_STAGES * DR_GROUP * tok_w; i += blockDim.x) smem[i] = 0.f;   // (rows beyond D stay zero)
+  for (int i = threadIdx.x; i < DR_STAGES * group * tok_w; i += blockDim.x) smem[i] = 0.f;   // (rows beyond D stay zero)
   __syncthreads();
 
   // a warp brings whole tokens, its lanes the pieces of a row: additions and shifts only (a lane's copies follow one
   // another in a chain of dependent index arithmetic, so a division per copy would cost more than the scan itself)
   auto fetch = [&](int g0, int buf) {
-    const int gn = min(DR_GROUP, n - g0);
-    float* dst0 = smem + (size_t)buf * DR_GROUP * tok_w;
+    const int gn = min(group, n - g0);
+    float* dst0 = smem + (size_t)buf * group * tok_w;
     for (int r = warp; r < gn; r += nwarps) {
       const float* row = ready + (size_t)(t0 + g0 + r) * W;
       const float* qrow = row + kvh * D;
@@ -166,18 +166,18 @@ delta_scan_kernel(float* __restrict__ out, const float* __restrict__ ready, cons
 
 #pragma unroll
   for (int st = 0; st < DR_STAGES - 1; ++st) {
-    if (st * DR_GROUP < n) fetch(st * DR_GROUP, st);
+    if (st * group < n) fetch(st * group, st);
     cp_async_commit();
   }
   int buf = 0;
-  for (int g0 = 0; g0 < n; g0 += DR_GROUP, buf = (buf + 1) % DR_STAGES) {
-    const int gn = min(DR_GROUP, n - g0);
+  for (int g0 = 0; g0 < n; g0 += group, buf = (buf + 1) % DR_STAGES) {
+    const int gn = min(group, n - g0);
     // (the buffer filled now is the one the group before this one was computed from: the barrier at its end freed it)
-    if (g0 + (DR_STAGES - 1) * DR_GROUP < n) fetch(g0 + (DR_STAGES - 1) * DR_GROUP, (buf + DR_STAGES - 1) % DR_STAGES);
+    if (g0 + (DR_STAGES - 1) * group < n) fetch(g0 + (DR_STAGES - 1) * group, (buf + DR_STAGES - 1) % DR_STAGES);
     cp_async_commit();
     cp_async_wait<DR_STAGES - 1>();
     __syncthreads();                                           // this group's rows are here
-    const float* grp = smem + (size_t)buf * DR_GROUP * tok_w;
+    const float* grp = smem + (size_t)buf * group * tok_w;
     for (int r = 0; r < gn; ++r) {
       const float* tok = grp + r * tok_w;
       const float4* qr = reinterpret_cast<const float4*>(tok + p * (R + DR_PAD));
@@ -308,10 +308,11 @@ TS_API int ts_delta_prepare(float* ready, const void* proj, int proj_stride, con
   TS_LAUNCH_CHECK();
 }
 
-// out: [T, H V] 32-bit.  proj: the raw projection rows (for the filter's new last inputs).
+// out: [T, H V] 32-bit.  proj: the raw projection rows (for the filter's new last inputs).  max_q_len: the most tokens a
+// request of the launch brings (0: unknown); it sizes the staging buffers.
 TS_API int ts_delta_scan(float* out, const float* ready, const void* proj, int proj_stride, float* state,
                          long long state_stride, const int* q_start, const int* slots, int B, int H, int G, int D, int V,
-                         int taps, int dtype, void* stream) {
+                         int taps, int max_q_len, int dtype, void* stream) {
   if (B <= 0) return 0;
   if (H <= 0 || G <= 0 || H % G || D <= 0 || V <= 0) TS_REFUSE(TS_ERR_SHAPE, "ts_delta_scan: %d heads over %d of %d x %d", H, G, D, V);
   if (taps < 1 || taps > 8) TS_REFUSE(TS_ERR_LIMIT, "ts_delta_scan: %d taps (1 to 8)", taps);
@@ -319,8 +320,11 @@ TS_API int ts_delta_scan(float* out, const float* ready, const void* proj, int p
   if (B > 65535 || H > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_delta_scan: %d requests / %d heads per launch", B, H);
   // rows of a column a lane holds: few rows mean more lanes a column, so more warps to hide one another's latencies
   // (one warp a scheduler waits out every dependent instruction), but a longer shuffle tree
+  // tokens staged at a time: no request of the launch brings more than max_q_len (0: unknown)
+  const int group = max_q_len > 0 ? min(DR_GROUP, max_q_len) : DR_GROUP;
   int R = g_delta_rows;
-  if (R != 8 && R != 16 && R != 32) R = D <= 256 ? 8 : (D <= 512 ? 16 : 32);
+  // (single tokens: one trip through the chain, so the fewest threads a column, which fit the chip in one wave)
+  if (R != 8 && R != 16 && R != 32) R = max_q_len == 1 ? 32 : (D <= 256 ? 8 : (D <= 512 ? 16 : 32));
   while (R < 32 && R * 32 < D) R *= 2;
   int P = 1;
   while (P * R < D) P <<= 1;
@@ -332,7 +336,7 @@ TS_API int ts_delta_scan(float* out, const float* ready, const void* proj, int p
   const int cols_block = nwarps * CW;
   const int W = 2 * G * D + H * V + 2 * H + G;
   const int vec4 = D % 4 == 0 && W % 4 == 0 && (G * D) % 4 == 0 && !((uintptr_t)ready & 15);
-  const size_t smem = sizeof(float) * DR_STAGES * DR_GROUP * ((size_t)2 * P * (R + DR_PAD) + ((cols_block + 3 + 3) & ~3));
+  const size_t smem = sizeof(float) * DR_STAGES * group * ((size_t)2 * P * (R + DR_PAD) + ((cols_block + 3 + 3) & ~3));
   if (smem > 200 * 1024) TS_REFUSE(TS_ERR_LIMIT, "ts_delta_scan: shared memory %zu", smem);
   cudaStream_t s = (cudaStream_t)stream;
   dim3 grid(ceil_div(V, cols_block), H, B);
@@ -345,7 +349,7 @@ TS_API int ts_delta_scan(float* out, const float* ready, const void* proj, int p
       configured = smem;                                                                                                 \
     }                                                                                                                    \
     ts_launch(delta_scan_kernel<RR>, dim3(grid), dim3(nwarps * 32), smem, s, out, ready, proj, proj_stride,              \
-              dtype == TS_BF16 ? 1 : 0, state, (size_t)state_stride, q_start, slots, H, G, D, V, taps, P, vec4);         \
+              dtype == TS_BF16 ? 1 : 0, state, (size_t)state_stride, q_start, slots, H, G, D, V, taps, P, vec4, group);  \
   } while (0)
   if (R == 32) TS_DS(32);
   else if (R == 16) TS_DS(16);

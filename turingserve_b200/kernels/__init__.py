@@ -122,7 +122,7 @@ class CudaOps:
             "ts_moe_combine": [P, P, P, P, I, I, I, I, P],
             "ts_moe_gather": [P, P, P, P, I, I, I, I, P],
             "ts_delta_prepare": [P, P, I, P, P, P, P, ctypes.c_longlong, P, P, P, I, I, I, I, I, I, F, I, P],
-            "ts_delta_scan": [P, P, P, I, P, ctypes.c_longlong, P, P, I, I, I, I, I, I, I, P],
+            "ts_delta_scan": [P, P, P, I, P, ctypes.c_longlong, P, P, I, I, I, I, I, I, I, I, P],
             "ts_head_gated_rmsnorm": [P, P, P, I, P, F, I, I, I, I, P],
             "ts_attention_biased": [P, I, I, P, I, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, P, I, I, P, P, I, P],
             "ts_attention_biased_mma": [P, I, I, P, I, I, P, P, P, P, P, I, I, I, I, I, I, I, I, F, F, P, I, I, P, P, I, P],
@@ -679,7 +679,7 @@ class CudaOps:
         inputs (from ``proj``) included."""
         self._check(self.lib.ts_delta_scan(_ptr(out), _ptr(ready), _ptr(proj), proj.stride(0), _ptr(state), state.stride(0),
                                            _ptr(step.q_start), _ptr(step.state_slots), step.num_requests, H, G, D, V, taps,
-                                           _code(proj.dtype), self._stream()), "delta_scan")
+                                           int(getattr(step, "max_q_len", 0) or 0), _code(proj.dtype), self._stream()), "delta_scan")
 
     def head_gated_rmsnorm(self, out, x, gate, weight, eps: float, H: int, V: int) -> None:
         """out [T, HV] = x / rms over each head's V * weight[V] * silu(gate); x float32; ``gate`` possibly a column
