@@ -256,7 +256,7 @@ head_gated_rmsnorm_kernel(T* __restrict__ out, const float* __restrict__ x, cons
   pdl_wait();
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  for (int h = warp; h < H; h += nwarps) {
+  for (int h = blockIdx.y * nwarps + warp; h < H; h += gridDim.y * nwarps) {      // a warp a head
     const float* xr = x + ((size_t)t * H + h) * V;
     const T* gr = gate + (size_t)t * gate_stride + (size_t)h * V;
     float ss = 0.f;
@@ -364,10 +364,12 @@ TS_API int ts_head_gated_rmsnorm(void* out, const float* x, const void* gate, in
                                  int T, int H, int V, int dtype, void* stream) {
   if (T <= 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
+  // few tokens: the heads of a token spread over blocks of four warps; many: one block a token
+  const int heads_y = T >= 512 ? 1 : min(ceil_div(H, 4), 65535);
   if (dtype == TS_F32)
-    ts_launch(head_gated_rmsnorm_kernel<float>, dim3(T), dim3(128), 0, s, (float*)out, x, (const float*)gate, gate_stride, w, eps, H, V);
+    ts_launch(head_gated_rmsnorm_kernel<float>, dim3(T, heads_y), dim3(128), 0, s, (float*)out, x, (const float*)gate, gate_stride, w, eps, H, V);
   else if (dtype == TS_BF16)
-    ts_launch(head_gated_rmsnorm_kernel<bf16>, dim3(T), dim3(128), 0, s, (bf16*)out, x, (const bf16*)gate, gate_stride, w, eps, H, V);
+    ts_launch(head_gated_rmsnorm_kernel<bf16>, dim3(T, heads_y), dim3(128), 0, s, (bf16*)out, x, (const bf16*)gate, gate_stride, w, eps, H, V);
   else
     TS_REFUSE(TS_ERR_DTYPE, "ts_head_gated_rmsnorm: dtype %d", dtype);
   TS_LAUNCH_CHECK();

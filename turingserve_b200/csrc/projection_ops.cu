@@ -6,7 +6,8 @@
 //   ts_latent_kv_write   one cached row a token: [rms(latent) * w | rotated key part]
 //   ts_rotate_pairs      rotation of neighbouring pairs (2i, 2i+1), angle = position * freq[i] in 32-bit, cosine and
 //                        sine times a magnitude; strided source and destination
-//   ts_batched_linear    out[t, h, :] = w[h] x[t, h, :], a product per head over strided rows (FFMA, fixed k order)
+//   ts_batched_linear    out[t, h, :] = w[h] x[t, h, :], a product per head over strided rows (FFMA, fixed k order; up to
+//                        16 rows: a warp an output column, streaming its weight row)
 #include "common.cuh"
 
 namespace {
@@ -190,6 +191,50 @@ batched_linear_kernel(T* __restrict__ out, int out_ts, int out_hs, const T* __re
   }
 }
 
+// Few rows: the weights are what is read.  A warp owns one output column of one head; its lanes stream that weight
+// row 16 bytes at a time and keep a partial sum for each of up to BLR_ROWS token rows (whose pieces come out of L1/L2,
+// shared by all warps); a lane's share of k and the order of the sums are the same whatever the number of rows.
+constexpr int BLR_ROWS = 8, BLR_WARPS = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(BLR_WARPS * 32)
+batched_linear_rows_kernel(T* __restrict__ out, int out_ts, int out_hs, const T* __restrict__ x, int x_ts, int x_hs,
+                           const T* __restrict__ w, int M, int N, int K) {
+  pdl_launch_dependents();
+  constexpr int PER = 16 / (int)sizeof(T);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int h = blockIdx.y, n = blockIdx.x * BLR_WARPS + warp;
+  if (n >= N) return;
+  const T* w_row = w + ((size_t)h * N + n) * K;
+  // (the weights are nobody's output: their first pieces are on their way before the wait for the predecessor)
+  uint4 first = make_uint4(0u, 0u, 0u, 0u);
+  if (lane * PER < K) first = *reinterpret_cast<const uint4*>(w_row + lane * PER);
+  pdl_wait();
+  for (int m0 = 0; m0 < M; m0 += BLR_ROWS) {
+    float acc[BLR_ROWS];
+#pragma unroll
+    for (int r = 0; r < BLR_ROWS; ++r) acc[r] = 0.f;
+    for (int k = lane * PER; k < K; k += 32 * PER) {
+      const uint4 wv = k == lane * PER ? first : *reinterpret_cast<const uint4*>(w_row + k);
+      const T* we = reinterpret_cast<const T*>(&wv);
+#pragma unroll
+      for (int r = 0; r < BLR_ROWS; ++r) {
+        if (m0 + r < M) {
+          const uint4 xv = *reinterpret_cast<const uint4*>(x + (size_t)(m0 + r) * x_ts + (size_t)h * x_hs + k);
+          const T* xe = reinterpret_cast<const T*>(&xv);
+#pragma unroll
+          for (int u = 0; u < PER; ++u) acc[r] = fmaf(to_f(xe[u]), to_f(we[u]), acc[r]);
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < BLR_ROWS; ++r) {
+      const float v = warp_sum(acc[r]);
+      if (lane == 0 && m0 + r < M) out[(size_t)(m0 + r) * out_ts + (size_t)h * out_hs + n] = from_f<T>(v);
+    }
+  }
+}
+
 int threads_for_row(int n) { return n >= 2048 ? 512 : (n >= 512 ? 256 : 128); }
 
 }  // namespace
@@ -257,6 +302,14 @@ TS_API int ts_batched_linear(void* out, int out_ts, int out_hs, const void* x, i
   dim3 grid(ceil_div(N, BL_N), ceil_div(T, BL_M), H);
   if (grid.y > 65535 || H > 65535) TS_REFUSE(TS_ERR_LIMIT, "ts_batched_linear: %d rows / %d heads per launch", T, H);
   cudaStream_t s = (cudaStream_t)stream;
+  const int per = dtype == TS_F32 ? 4 : 8;
+  if (T <= 2 * BLR_ROWS && K % per == 0 && x_ts % per == 0 && x_hs % per == 0 && !((uintptr_t)x & 15) && !((uintptr_t)w & 15)) {
+    dim3 rows_grid(ceil_div(N, BLR_WARPS), H);
+    TS_BY_TYPE("ts_batched_linear",
+               ts_launch(batched_linear_rows_kernel<TT>, dim3(rows_grid), dim3(BLR_WARPS * 32), 0, s, (TT*)out, out_ts, out_hs,
+                         (const TT*)x, x_ts, x_hs, (const TT*)w, T, N, K));
+    TS_LAUNCH_CHECK();
+  }
   TS_BY_TYPE("ts_batched_linear",
              ts_launch(batched_linear_kernel<TT>, dim3(grid), dim3(256), 0, s, (TT*)out, out_ts, out_hs, (const TT*)x, x_ts, x_hs,
                        (const TT*)w, T, N, K));

@@ -726,12 +726,12 @@ class CudaOps:
                                              _code(src.dtype), self._stream()), "rotate_pairs")
 
     # bfloat16 per-head products with at least this many rows go to the library's batched product
-    batched_library_rows = int(os.environ.get("TURINGSERVE_B200_BATCHED_LIBRARY_ROWS", "64"))
+    batched_library_rows = int(os.environ.get("TURINGSERVE_B200_BATCHED_LIBRARY_ROWS", "17"))
 
     def batched_linear(self, out, x, w) -> None:
         """out[t, h, :] = w[h] x[t, h, :]: ``x`` [T, H, K] and ``out`` [T, H, N] views with unit last stride,
-        ``w`` [H, N, K] contiguous.  float32: this library's FFMA kernel (fixed k order); bfloat16 with many rows:
-        the vendor's batched product."""
+        ``w`` [H, N, K] contiguous.  This library's kernels (up to 16 rows: a warp an output column, streaming
+        its weight row; float32 above: FFMA tiles, fixed k order); bfloat16 with more rows: the vendor's batched product."""
         T, H, K = x.shape
         N = w.shape[1]
         if out.stride(2) != 1 or x.stride(2) != 1 or not w.is_contiguous():
