@@ -9,11 +9,11 @@ The design, in this file's notation (x is the residual stream, one row a token, 
              another layer's tensors and still keeps memory of its own)
 * delta:     q, k, v = silu(conv(Wq h)), silu(conv(Wk h)), silu(conv(Wv h)), conv a causal filter of a few
              taps per channel; q, k to unit length per head, q / sqrt(dim); b = sigmoid(Wb h);
-             g = exp(-exp(A) softplus(Wa h + dt)); per head S <- g S; u = b (v - S^T k); S <- S + k u^T;
-             o = S^T q; o / rms(o) * w_norm * silu(Wg h); Wo
+             g = exp(-exp(A) softplus(Wa h + dt)); head by head the memory M fades, is corrected and read:
+             M <- g M; e = b (v - M^T k); M <- M + k e^T; y = M^T q; y / rms(y) * w_norm * silu(Wg h); Wo
 * attention: q = Wq h, k = Wk h, values = k; q and k normed over the WHOLE row (all heads at once) with a
-             weight; q *= 1 + c ln(floor((p+1)/every) + 1); s = cap tanh(q.k scale / cap) - slope_h (i - j),
-             slope_h = 2^(-8 (h+1) / H); keys i - w < j <= i; softmax; Wo
+             weight; q *= 1 + c ln(floor((p+1)/every) + 1); s = cap tanh(q.k scale / cap) - m_h (i - j), with
+             the slopes m_h = 2^(-8 (h+1) / H) for h = 0 .. H-1; keys i - w < j <= i; softmax; Wo
 * latent:    cq = rms(Wdq h) * w; q = Wuq cq, per head [plain | rotated]; Wdkv h = [c_raw | kr];
              c = rms(c_raw) * w; per head k = [Wuk c | rot(kr)], v = Wuv c; causal softmax of q.k scale; Wo.
              rot: interleaved pairs, YaRN-blended frequencies, cos and sin times 0.1 ln(factor) + 1
@@ -138,13 +138,13 @@ def yarn_angles(rot: dict, positions: torch.Tensor):
     mag = 1.0
     sc = rot.get("scaling")
     if sc:
-        def place(t):
-            return dims * math.log(sc["original"] / (2 * math.pi * t)) / (2 * math.log(base))
-        lo = max(math.floor(place(sc["fast"])), 0)
-        hi = min(math.ceil(place(sc["slow"])), dims - 1)
-        ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0, 1)
-        f = f / sc["factor"] * ramp + f * (1 - ramp)
-        mag = 0.1 * math.log(sc["factor"]) + 1.0
+        def pair_at(turns):
+            return dims * math.log(sc["original"] / (2 * math.pi * turns)) / (2 * math.log(base))
+        begin = max(math.floor(pair_at(sc["fast"])), 0)
+        end = min(math.ceil(pair_at(sc["slow"])), dims - 1)
+        t = ((i - begin) / max(end - begin, 0.001)).clamp(0, 1)
+        f = (1 - t) * f + t * (f / sc["factor"])
+        mag = 1.0 + 0.1 * math.log(sc["factor"])
     a = positions.to(torch.float64)[:, None] * f[None, :]
     return torch.cos(a) * mag, torch.sin(a) * mag
 

@@ -115,10 +115,13 @@ class DiffAttentionSpec:
 class YarnRotarySpec:
     """Rotary position encoding over pairs of neighbouring dimensions (2i, 2i+1) of the first ``dims``
     dimensions of a vector, angle = position * f_i with f_i = base^(-2i/dims).  With ``factor`` set the
-    frequencies are blended (YaRN): with place(t) = dims ln(original / (2 pi t)) / (2 ln base),
-    lo = max(floor(place(fast)), 0), hi = min(ceil(place(slow)), dims - 1) and
-    ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) the frequency is f_i / factor * ramp_i + f_i (1 - ramp_i),
-    and cosine and sine are both multiplied by 0.1 ln(factor) + 1."""
+    frequencies are blended (YaRN) between the plain ones and the ones slowed by ``factor``: a pair that turns
+    ``fast`` times or more within ``original`` positions keeps f_i, one that turns ``slow`` times or fewer gets
+    f_i / factor, and between them the share of the slowed frequency grows linearly with the pair's index.  The
+    index at which a pair turns r times is idx(r) = dims * log(original / (2 * pi * r)) / (2 * log(base)); the
+    blend starts at first = max(floor(idx(fast)), 0) and is complete at last = min(ceil(idx(slow)), dims - 1):
+    share_i = min(max((i - first) / max(last - first, 0.001), 0), 1).  Cosine and sine are both scaled by
+    1 + 0.1 * log(factor)."""
 
     base: float
     dims: int
@@ -131,12 +134,14 @@ class YarnRotarySpec:
 
 @dataclass(frozen=True)
 class DeltaRuleSpec:
-    """Gated delta rule: a matrix state per head, S <- g S; u = b (v - S^T k); S <- S + k u^T; o = S^T q, with
-    q, k, v = silu(short causal filter(projection)), q and k brought to unit length per head (``unit_eps``
-    inside the root) and q divided by sqrt(key_dim), b = sigmoid(projection),
-    g = exp(-exp(A) softplus(projection + dt)); query/key head floor(h / (heads / kv_heads)) serves head h;
-    each head's o is divided by its root mean square, multiplied by a weight shared by the heads and by
-    silu(gate projection); then the output projection."""
+    """Gated delta rule: a matrix memory M [key_dim, value_dim] per head that a token first fades, then corrects
+    by what it gets wrong about the token's key, then reads:
+        M <- d M;   e = w (v - M^T k);   M <- M + k e^T;   y = M^T q,
+    with q, k, v = silu(short causal filter(projection)), q and k of unit length per head (``unit_eps`` inside
+    the root), q also over sqrt(key_dim), write strength w = sigmoid(projection) and fade
+    d = exp(-exp(A) * softplus(projection + dt)).  Heads are served by ``num_kv_heads`` query/key heads in equal
+    groups.  Every head's y is normed by its own root mean square, scaled by a weight common to the heads and
+    gated by silu(gate projection); then the output projection."""
 
     num_heads: int
     num_kv_heads: int
@@ -173,8 +178,8 @@ class CappedAttentionSpec:
 class LatentAttentionSpec:
     """Attention through low-rank latents: queries W_uq rms(W_dq h), per head [``nope_dim`` plain |
     ``rope_dim`` rotated]; per token one latent c = rms(first ``kv_rank`` rows of W_dkv h) and one rotated key
-    part (the last ``rope_dim`` rows) shared by all heads; per head keys W_uk c and values W_uv c.  Causal
-    softmax of (q_plain . k_plain + q_rot . k_rot) * scale.  Only c and the rotated key part are cached."""
+    part (the last ``rope_dim`` rows) that every head uses; head by head the keys are W_uk c and the values W_uv c.
+    Causal softmax of (q_plain . k_plain + q_rot . k_rot) * scale.  The cache holds c and the rotated key part only."""
 
     num_heads: int
     nope_dim: int

@@ -1,7 +1,7 @@
-// The gated delta rule: for every request and head a matrix state S [D, V] in 32-bit that lives in a state slot
-// between steps.  Per token, with q and k of unit length (q also divided by sqrt(D)), a decay g in (0, 1) and a
-// write strength beta in (0, 1):
-//     S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q        (o sees the token's own write).
+// The gated delta rule: for every request and head a matrix memory M [D, V] in 32-bit that lives in a state slot
+// between steps (S in the code).  Per token, with q and k of unit length (q also over sqrt(D)), a fade d in (0, 1)
+// (g in the code) and a write strength w in (0, 1) (beta):
+//     M <- d M;   e = w (v - M^T k);   M <- M + k e^T;   y = M^T q          (y comes after the token's own write).
 // q, k and v are a fused projection's columns after a causal filter of a few taps per channel and SiLU; the
 // filter's last taps - 1 inputs are kept behind S in the same slot: [H D V | (taps - 1) x C], C = 2 G D + H V.
 //

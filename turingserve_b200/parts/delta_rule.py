@@ -2,13 +2,13 @@
 
 One fused projection gives, per token, [q (G D) | k (G D) | v (H V) | gate (H V) | b (H) | a (H)].  q, k and v
 pass a causal filter of a few taps per channel and SiLU; q and k are brought to unit length per head and q is
-divided by sqrt(D); beta = sigmoid(b); g = exp(-exp(A) softplus(a + dt)).  Per head, in 32-bit:
-S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q (the read-out sees the token's own write).  Each
-head's o is divided by its root mean square, multiplied by a weight shared by the heads and by silu(gate);
-then the output projection.
+divided by sqrt(D); write strength w = sigmoid(b); fade d = exp(-exp(A) softplus(a + dt)).  Per head, in 32-bit,
+with M the head's memory [D, V]:   M <- d M;   e = w (v - M^T k);   M <- M + k e^T;   y = M^T q   (the read-out
+comes after the token's own write).  Every head's y is normed by its own root mean square, scaled by a weight
+common to the heads and gated by silu(gate); then the output projection.
 
 Nothing is cached per token.  The mixer declares one flat 32-bit state per request:
-[H D V values of S | (taps - 1) x (2 G D + H V) last filter inputs], zeroed when the request is admitted, so
+[H D V values of M | (taps - 1) x (2 G D + H V) last filter inputs], zeroed when the request is admitted, so
 the first portion needs no branch and a captured step's padding rows update the null slot.
 """
 

@@ -44,13 +44,14 @@ class PairRotaryEncoding:
         f = base ** (-2.0 * i / self.dims)
         self.magnitude = 1.0
         if spec.factor:
-            def place(t: float) -> float:
-                return self.dims * math.log(spec.original / (2.0 * math.pi * t)) / (2.0 * math.log(base))
-            lo = max(math.floor(place(spec.fast)), 0)
-            hi = min(math.ceil(place(spec.slow)), self.dims - 1)
-            ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
-            f = f / float(spec.factor) * ramp + f * (1.0 - ramp)
-            self.magnitude = 0.1 * math.log(float(spec.factor)) + 1.0
+            def index_of(turns: float) -> float:
+                """The (fractional) pair index whose frequency turns ``turns`` times within ``original`` positions."""
+                return self.dims * math.log(spec.original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+            first = max(math.floor(index_of(spec.fast)), 0)
+            last = min(math.ceil(index_of(spec.slow)), self.dims - 1)
+            share = ((i - first) / max(last - first, 0.001)).clamp(0.0, 1.0)      # of the slowed frequency
+            f = f * (1.0 - share) + (f / float(spec.factor)) * share
+            self.magnitude = 1.0 + 0.1 * math.log(float(spec.factor))
         self.freq = f.to(torch.float32).to(ctx.device).contiguous()
 
 
